@@ -1,0 +1,161 @@
+/*
+ * b200_gemm.h — C ABI of the B200 (sm_100a) half-precision GEMM library.
+ *
+ * The library computes C = A * B (no alpha/beta) for four (output, input) type pairs
+ * and every row-/column-major combination of A (M x K), B (K x N) and C (M x N), single
+ * or strided-batched, with dense-packed matrices (leading dimension == the contiguous
+ * extent) and batch strides M*K, K*N and M*N elements.
+ *
+ * Two groups of entry points:
+ *
+ *  1. The four `rocm_wmma_gemm_<out>_<in>` symbols.  Name, argument order and argument
+ *     meaning are those of the reference library's per-architecture shared object, so a
+ *     host program that dlopen()s that object and dlsym()s these four names binds here
+ *     unchanged.  They return void and never throw; a failure is recorded and can be
+ *     read with b200_gemm_last_status() / b200_gemm_last_error().
+ *
+ *  2. `b200_gemm_*` twins that return a status code, plus helpers the reference does not
+ *     have (host-buffer call, explicit config, column-slab partition, device status).
+ *
+ * All pointers named C/A/B in group 1 and in b200_gemm_<out>_<in> are DEVICE pointers.
+ * `stream` is a POINTER TO a cudaStream_t (the reference passes `&stream`); NULL means
+ * the default stream.  Layout ints: 0 = row-major, 1 = column-major.
+ */
+#ifndef B200_GEMM_H
+#define B200_GEMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------ */
+enum b200_gemm_status {
+    B200_GEMM_OK               = 0,
+    B200_GEMM_ERR_BAD_LAYOUT   = 1, /* a layout int is not 0 or 1 (the reference ignores the call) */
+    B200_GEMM_ERR_NULL_POINTER = 2,
+    B200_GEMM_ERR_BAD_SIZE     = 3, /* a dimension does not fit 31 bits, or batch_count == 0 */
+    B200_GEMM_ERR_MISALIGNED   = 4, /* a base pointer is not aligned to its element size */
+    B200_GEMM_ERR_NO_DEVICE    = 5, /* no CUDA device, or the current device is not sm_100 */
+    B200_GEMM_ERR_CUDA         = 6, /* a CUDA runtime/driver call failed; see last_error */
+    B200_GEMM_ERR_BAD_CONFIG   = 7, /* explicit config outside the compiled variant set */
+    B200_GEMM_ERR_DEVICE_WAIT  = 8, /* a kernel gave up on a bounded wait (device status) */
+    B200_GEMM_ERR_TOO_LARGE    = 9  /* request exceeds a fixed-capacity entry point's limit */
+};
+
+/* ---- group 1: the reference's C ABI ----------------------------------------------------
+ * Replaces rocm_wmma_gemm/src/gemm.cpp:207-250 (DEFINE_C_DISPATCH) of the reference, which
+ * rocm_wmma_gemm/include/rocm_wmma_gemm/kernel_loader.hpp:91-113 resolves by name.
+ * Suffix is <out>_<in>.  C: M x N, A: M x K, B: K x N; batch strides M*N, M*K, K*N.
+ */
+void rocm_wmma_gemm_f16_f16(void* C, void* A, void* B, size_t M, size_t N, size_t K,
+                            size_t batch_count, int layout_c, int layout_a, int layout_b,
+                            void* stream);
+void rocm_wmma_gemm_f32_f16(void* C, void* A, void* B, size_t M, size_t N, size_t K,
+                            size_t batch_count, int layout_c, int layout_a, int layout_b,
+                            void* stream);
+void rocm_wmma_gemm_bf16_bf16(void* C, void* A, void* B, size_t M, size_t N, size_t K,
+                              size_t batch_count, int layout_c, int layout_a, int layout_b,
+                              void* stream);
+void rocm_wmma_gemm_f32_bf16(void* C, void* A, void* B, size_t M, size_t N, size_t K,
+                             size_t batch_count, int layout_c, int layout_a, int layout_b,
+                             void* stream);
+
+/* ---- group 2: status-returning twins ----------------------------------------------------
+ * Same arguments as group 1 (reference: rocm_wmma_gemm/src/gemm.cpp:219-245); the return
+ * value is a b200_gemm_status.  The call is asynchronous on `*stream`.
+ */
+int b200_gemm_f16_f16(void* C, void* A, void* B, size_t M, size_t N, size_t K,
+                      size_t batch_count, int layout_c, int layout_a, int layout_b, void* stream);
+int b200_gemm_f32_f16(void* C, void* A, void* B, size_t M, size_t N, size_t K,
+                      size_t batch_count, int layout_c, int layout_a, int layout_b, void* stream);
+int b200_gemm_bf16_bf16(void* C, void* A, void* B, size_t M, size_t N, size_t K,
+                        size_t batch_count, int layout_c, int layout_a, int layout_b, void* stream);
+int b200_gemm_f32_bf16(void* C, void* A, void* B, size_t M, size_t N, size_t K,
+                       size_t batch_count, int layout_c, int layout_a, int layout_b, void* stream);
+
+/* Type-pair index used by the generic entry points below; the numbering is the reference's
+ * type_idx (rocm_wmma_gemm/include/rocm_wmma_gemm/kernel_launcher.hpp:78-84):
+ * 0 = f16<-f16, 1 = f32<-f16, 2 = bf16<-bf16, 3 = f32<-bf16. */
+enum b200_gemm_types {
+    B200_GEMM_F16_F16   = 0,
+    B200_GEMM_F32_F16   = 1,
+    B200_GEMM_BF16_BF16 = 2,
+    B200_GEMM_F32_BF16  = 3
+};
+
+/* Tunable launch configuration: the B200 counterpart of the reference's per-entry `config`
+ * object {warps_m, warps_n, warp_tile_m, warp_tile_n, swizzle, bits}
+ * (rocm_wmma_gemm/config/gemm_config_gfx1100_f16.json:1-22; struct gemm_params generated by
+ * rocm_wmma_gemm/config/generate_config.py:94-103).
+ *   tile_m   rows of C per CTA (per CTA pair when cluster == 2): 128, or 256 with cluster 2
+ *   tile_n   columns of C per CTA / CTA pair: 64, 128 or 256
+ *   stages   depth of the TMA -> shared-memory ring (2 .. 8, clamped to what fits)
+ *   cluster  1 = one CTA per tile, 2 = a CTA pair shares one tile (cta_group::2 MMA)
+ *   split_k  number of K partitions reduced through an f32 workspace (1 = none)
+ *   raster   tile-rows per raster band (the reference's `swizzle` key); 0 = column sweep
+ */
+typedef struct b200_gemm_config {
+    int tile_m;
+    int tile_n;
+    int stages;
+    int cluster;
+    int split_k;
+    int raster;
+} b200_gemm_config;
+
+/* C = A*B with an explicit configuration (cfg == NULL: the tuned table decides, exactly as
+ * the four fixed-type entry points do).  Used by the tuner and the benchmarks; counterpart
+ * of the tuner's "one instantiation chosen by CLI parameters"
+ * (rocm_wmma_gemm/config/tuner.cpp:458-466). */
+int b200_gemm_ex(int types, void* C, const void* A, const void* B, size_t M, size_t N, size_t K,
+                 size_t batch_count, int layout_c, int layout_a, int layout_b, void* stream,
+                 const b200_gemm_config* cfg);
+
+/* The configuration the tuned table selects for a problem: exact (M,N,K,type_group,layouts)
+ * match, else exact match in the 16-bit-output group, else nearest K then nearest (M,N)
+ * within the same layout triple, else the default.  Counterpart of
+ * detail::find_best_config / get_gemm_params
+ * (rocm_wmma_gemm/config/generate_config.py:174-303).  Pure host code, no GPU needed.
+ * Returns the index of the chosen entry of the compiled config list (>= 0). */
+int b200_gemm_select_config(size_t M, size_t N, size_t K, int types, int layout_c, int layout_a,
+                            int layout_b, b200_gemm_config* out);
+
+/* Host-buffer call: A, B, C are HOST pointers (pageable or pinned).  Copies A and B to the
+ * device, runs the GEMM, copies C back and synchronises; device buffers are cached per
+ * device and grow on demand.  This is the path a caller without device memory of its own
+ * uses, and the one the end-to-end benchmark times.  No reference counterpart (the
+ * reference's tests do the copies themselves, test/gemm/test_float_accum.cpp:95-119). */
+int b200_gemm_host(int types, void* C, const void* A, const void* B, size_t M, size_t N, size_t K,
+                   size_t batch_count, int layout_c, int layout_a, int layout_b);
+
+/* Column-slab partition of C = A*B over `world` devices with A replicated: device `rank`
+ * owns columns [*n_begin, *n_begin + *n_count) of B and C.  Slab widths are multiples of
+ * `align` columns except the last.  No reference counterpart (the reference is single-GPU). */
+int b200_gemm_slab(size_t N, int world, int rank, size_t align, size_t* n_begin, size_t* n_count);
+
+/* Bytes of f32 split-K workspace a call would use (0 when the chosen config has split_k 1). */
+size_t b200_gemm_workspace_bytes(int types, size_t M, size_t N, size_t K, size_t batch_count,
+                                 int layout_c, int layout_a, int layout_b,
+                                 const b200_gemm_config* cfg);
+
+/* Synchronises the current device and returns B200_GEMM_ERR_DEVICE_WAIT if any kernel of
+ * this library has given up on a bounded wait since the last call (then clears the flag),
+ * else B200_GEMM_OK.  `detail`, if not NULL, receives the raw device status word. */
+int b200_gemm_device_status(unsigned int* detail);
+
+/* Status / message of the last failing call on the calling thread (group 1 included). */
+int         b200_gemm_last_status(void);
+const char* b200_gemm_last_error(void);
+
+/* Library version and the number of kernel launches issued so far by this process
+ * (used by the benchmark to report how many of its own kernels ran in a timed region). */
+const char*        b200_gemm_version(void);
+unsigned long long b200_gemm_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_GEMM_H */

@@ -1,0 +1,485 @@
+// Device kernels of the B200 GEMM library.
+//
+//   gemm_umma_kernel   persistent, warp-specialised tcgen05 GEMM, one CTA per 128 x BN tile
+//   splitk_reduce_kernel   deterministic sum of split-K partials + conversion to the output type
+//   gemm_generic_kernel    CUDA-core GEMM for shapes whose leading dimensions TMA cannot address
+//
+// "Kernel view" of a problem: D (Mk x Nk, row-major) = A' (Mk x K) * B' (K x Nk) where each
+// operand is either K-major (K contiguous) or MN-major (its M or N extent contiguous).  The
+// host maps the reference's eight layout combinations onto this view; a column-major C is
+// the row-major C^T = B^T * A^T, i.e. the operands swap roles
+// (reference semantics: rocm_wmma_gemm/include/rocm_wmma_gemm/gemm.hpp:50-73).
+#pragma once
+
+#include "ptx_sm100.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace b200 {
+
+// Output element kinds of the epilogue.
+enum : int { OUT_F32 = 0, OUT_F16 = 1, OUT_BF16 = 2 };
+
+// Bits of the device status word (set when a bounded wait expires).
+enum : unsigned int {
+    ST_PRODUCER_WAIT = 1u,  // TMA producer waiting for a free ring slot
+    ST_MMA_WAIT_FULL = 2u,  // MMA issuer waiting for a filled ring slot
+    ST_MMA_WAIT_ACC  = 4u,  // MMA issuer waiting for a drained accumulator
+    ST_EPI_WAIT      = 8u,  // epilogue waiting for a finished accumulator
+    ST_DRAIN_WAIT    = 16u, // tail waiting for outstanding MMAs / loads
+    ST_PEER_WAIT     = 32u  // CTA-pair handshake
+};
+
+struct GemmParams {
+    uint32_t M, N, K;      // kernel-view extents
+    uint32_t batch;        // batch count
+    uint32_t m_tiles;      // ceil(M / 128)
+    uint32_t n_tiles;      // ceil(N / BN)
+    uint32_t k_blocks;     // ceil(K / 64)
+    uint32_t split_k;      // K partitions (>= 1); every partition owns >= 1 k-block
+    uint32_t kb_per_split; // k-blocks per partition
+    uint32_t group_m;      // raster band height in tiles (0 = sweep columns)
+    uint32_t num_work;     // batch * split_k * m_tiles * n_tiles
+    uint32_t a_mn_major;   // 0: A' K-major, 1: A' M-major
+    uint32_t b_mn_major;   // 0: B' K-major, 1: B' N-major
+    uint32_t idesc;        // tcgen05 instruction descriptor
+    uint32_t stages;       // ring depth actually used (<= MAX_STAGES)
+    unsigned int* status;  // device status word
+};
+
+constexpr int      BLOCK_M        = 128;
+constexpr int      BLOCK_K        = 64; // 64 x 2 B = one 128-byte swizzle row
+constexpr int      UMMA_K         = 16;
+constexpr int      MAX_STAGES     = 8;
+constexpr int      GEMM_THREADS   = 192; // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
+constexpr uint32_t A_TILE_BYTES   = BLOCK_M * BLOCK_K * 2;
+constexpr uint32_t EPI_BUF_BYTES  = 32 * 128; // one warp's 32 rows x 128 B
+constexpr uint32_t EPI_BYTES      = 4 * 2 * EPI_BUF_BYTES;
+constexpr uint64_t WAIT_LIMIT_NS  = 2000000000ull; // 2 s per bounded wait
+
+__host__ __device__ constexpr uint32_t stage_bytes(int bn)
+{
+    return A_TILE_BYTES + static_cast<uint32_t>(bn) * BLOCK_K * 2;
+}
+
+// Dynamic shared memory a launch needs (1 KiB slack for manual 1024-byte alignment).
+__host__ __device__ constexpr uint32_t gemm_smem_bytes(int bn, int stages)
+{
+    return static_cast<uint32_t>(stages) * stage_bytes(bn) + EPI_BYTES + 1024;
+}
+
+// Waits for the phase with the given parity; gives up after WAIT_LIMIT_NS or as soon as
+// another role of this CTA has given up.  Returns false on give-up.
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity,
+                                             volatile uint32_t* s_abort, unsigned int* status,
+                                             unsigned int code)
+{
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0    = ptx::global_timer_ns();
+    uint32_t       spins = 0;
+    while (true) {
+        if (ptx::mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 31u) == 0u) {
+            if (*s_abort != 0u) return false;
+            if (ptx::global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+                *s_abort = 1u;
+                atomicOr(status, code);
+                return false;
+            }
+        }
+    }
+}
+
+struct WorkCoord {
+    uint32_t m0, n0;   // first row / column of the tile
+    uint32_t z_in;     // batch index (third TMA coordinate of A' and B')
+    uint32_t z_out;    // third TMA coordinate of D: batch * split_k + split
+    uint32_t kb0, kb1; // k-block range
+};
+
+__device__ __forceinline__ WorkCoord decode_work(const GemmParams& p, uint32_t w, int bn)
+{
+    const uint32_t tiles = p.m_tiles * p.n_tiles;
+    const uint32_t t     = w % tiles;
+    const uint32_t r     = w / tiles;
+    const uint32_t split = r % p.split_k;
+    const uint32_t b     = r / p.split_k;
+    uint32_t       m_idx, n_idx;
+    if (p.group_m == 0u) {
+        m_idx = t % p.m_tiles;
+        n_idx = t / p.m_tiles;
+    } else {
+        const uint32_t per_group = p.group_m * p.n_tiles;
+        const uint32_t g         = t / per_group;
+        const uint32_t first_m   = g * p.group_m;
+        const uint32_t gsize     = min(p.group_m, p.m_tiles - first_m);
+        const uint32_t in_g      = t - g * per_group;
+        m_idx                    = first_m + in_g % gsize;
+        n_idx                    = in_g / gsize;
+    }
+    WorkCoord c;
+    c.m0    = m_idx * BLOCK_M;
+    c.n0    = n_idx * static_cast<uint32_t>(bn);
+    c.z_in  = b;
+    c.z_out = b * p.split_k + split;
+    c.kb0   = split * p.kb_per_split;
+    c.kb1   = min(p.k_blocks, c.kb0 + p.kb_per_split);
+    return c;
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
+                                             uint32_t d)
+{
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c),
+                 "r"(d)
+                 : "memory");
+}
+
+template <int OUT>
+__device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits)
+{
+    const float lo = __uint_as_float(lo_bits);
+    const float hi = __uint_as_float(hi_bits);
+    if constexpr (OUT == OUT_F16) {
+        const __half2 h = __floats2half2_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    } else {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&h);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Persistent tcgen05 GEMM, one CTA per 128 x BN output tile.
+//
+//   warp 0 (one lane)  TMA producer: fills a `stages`-deep ring of {A' 128x64, B' BNx64} tiles
+//                      (128-byte swizzle), one mbarrier pair (full/empty) per slot.
+//   warp 1 (one lane)  MMA issuer: 4 x tcgen05.mma (K = 16 each) per slot into one of two
+//                      TMEM accumulators (BN f32 columns each); tcgen05.commit releases the
+//                      slot and, after the last k-block, publishes the accumulator.
+//   warps 2..5         epilogue: tcgen05.ld 32 lanes x 32 columns, convert, swizzled store to a
+//                      per-warp staging buffer, TMA store of 32 rows x 128 B; the accumulator
+//                      is handed back as soon as its last column chunk is in registers, so the
+//                      epilogue of tile i overlaps the main loop of tile i + 1.
+//
+// Edges: TMA zero-fills out-of-range loads (M, N and K tails) and clips stores.
+// ---------------------------------------------------------------------------------------------
+template <int BN, int OUT>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA,
+                     const __grid_constant__ CUtensorMap tmB,
+                     const __grid_constant__ CUtensorMap tmD, const GemmParams p)
+{
+    static_assert(BN == 64 || BN == 128 || BN == 256, "BN must be 64, 128 or 256");
+    constexpr uint32_t B_TILE_BYTES = BN * BLOCK_K * 2;
+    constexpr uint32_t STAGE_BYTES  = A_TILE_BYTES + B_TILE_BYTES;
+    constexpr uint32_t TMEM_COLS    = 2 * BN; // two accumulators; power of two >= 32
+    constexpr int      OUT_BYTES    = (OUT == OUT_F32) ? 4 : 2;
+    constexpr int      CH           = 128 / OUT_BYTES; // output columns per 128-byte chunk
+    constexpr int      NCHUNK       = BN / CH;
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t s_full[MAX_STAGES];
+    __shared__ __align__(8) uint64_t s_empty[MAX_STAGES];
+    __shared__ __align__(8) uint64_t s_tfull[2];
+    __shared__ __align__(8) uint64_t s_tempty[2];
+    __shared__ __align__(8) uint64_t s_drain;
+    __shared__ uint32_t              s_tmem_base;
+    __shared__ volatile uint32_t     s_abort;
+
+    const uint32_t tid    = threadIdx.x;
+    const uint32_t warp   = tid >> 5;
+    const uint32_t lane   = tid & 31u;
+    const uint32_t stages = p.stages;
+
+    const uint32_t ring = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u; // ring of operand tiles
+    const uint32_t epi  = ring + stages * STAGE_BYTES;                // epilogue staging
+
+    if (tid == 0) {
+        ptx::prefetch_tensormap(&tmA);
+        ptx::prefetch_tensormap(&tmB);
+        ptx::prefetch_tensormap(&tmD);
+        for (uint32_t s = 0; s < stages; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&s_full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&s_empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(ptx::smem_u32(&s_tfull[b]), 1);
+            ptx::mbar_init(ptx::smem_u32(&s_tempty[b]), 4);
+        }
+        ptx::mbar_init(ptx::smem_u32(&s_drain), 1);
+        s_abort = 0u;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc<1>(ptx::smem_u32(&s_tmem_base), TMEM_COLS);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = s_tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, issued = 0;
+            bool     ok = true;
+            for (uint32_t w = blockIdx.x; ok && w < p.num_work; w += gridDim.x) {
+                const WorkCoord c = decode_work(p, w, BN);
+                for (uint32_t kb = c.kb0; kb < c.kb1; ++kb) {
+                    ok = bounded_wait(ptx::smem_u32(&s_empty[stage]), phase ^ 1u, &s_abort,
+                                      p.status, ST_PRODUCER_WAIT);
+                    if (!ok) break;
+                    const uint32_t bar = ptx::smem_u32(&s_full[stage]);
+                    const uint32_t sa  = ring + stage * STAGE_BYTES;
+                    const uint32_t sb  = sa + A_TILE_BYTES;
+                    const int32_t  k0  = static_cast<int32_t>(kb * BLOCK_K);
+                    ptx::mbar_expect_tx(bar, STAGE_BYTES);
+                    if (p.a_mn_major == 0u) {
+                        ptx::tma_load_3d(sa, &tmA, bar, k0, c.m0, c.z_in);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BLOCK_M / 64; ++j)
+                            ptx::tma_load_3d(sa + j * (64 * BLOCK_K * 2), &tmA, bar,
+                                             c.m0 + j * 64, k0, c.z_in);
+                    }
+                    if (p.b_mn_major == 0u) {
+                        ptx::tma_load_3d(sb, &tmB, bar, k0, c.n0, c.z_in);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j)
+                            ptx::tma_load_3d(sb + j * (64 * BLOCK_K * 2), &tmB, bar,
+                                             c.n0 + j * 64, k0, c.z_in);
+                    }
+                    ++issued;
+                    if (++stage == stages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (s_abort != 0u) {
+                // Gave up somewhere: let the loads already in flight land before the CTA exits.
+                const uint32_t pending = min(issued, stages);
+                for (uint32_t i = 0; i < pending; ++i) {
+                    if (stage == 0) {
+                        stage = stages;
+                        phase ^= 1u;
+                    }
+                    --stage;
+                    const uint64_t t0 = ptx::global_timer_ns();
+                    while (!ptx::mbar_try_wait(ptx::smem_u32(&s_full[stage]), phase)) {
+                        if (ptx::global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+                            atomicOr(p.status, ST_DRAIN_WAIT);
+                            break;
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            // K-major swizzled tiles ignore the leading offset (canonical value: 16 bytes).
+            const uint32_t a_lbo   = p.a_mn_major ? 64u * BLOCK_K * 2u : 16u;
+            const uint32_t b_lbo   = p.b_mn_major ? 64u * BLOCK_K * 2u : 16u;
+            // Descriptor start-address step (16-byte units) per K = 16 slice.
+            const uint32_t a_kstep = p.a_mn_major ? (2u * 1024u) >> 4 : (UMMA_K * 2u) >> 4;
+            const uint32_t b_kstep = p.b_mn_major ? (2u * 1024u) >> 4 : (UMMA_K * 2u) >> 4;
+            uint32_t       stage = 0, phase = 0, it = 0;
+            bool           ok = true;
+            for (uint32_t w = blockIdx.x; ok && w < p.num_work; w += gridDim.x, ++it) {
+                const WorkCoord c      = decode_work(p, w, BN);
+                const uint32_t  buf    = it & 1u;
+                const uint32_t  aphase = (it >> 1) & 1u;
+                ok = bounded_wait(ptx::smem_u32(&s_tempty[buf]), aphase ^ 1u, &s_abort, p.status,
+                                  ST_MMA_WAIT_ACC);
+                if (!ok) break;
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (uint32_t kb = c.kb0; kb < c.kb1; ++kb) {
+                    ok = bounded_wait(ptx::smem_u32(&s_full[stage]), phase, &s_abort, p.status,
+                                      ST_MMA_WAIT_FULL);
+                    if (!ok) break;
+                    ptx::tc_fence_after();
+                    const uint32_t sa = ring + stage * STAGE_BYTES;
+                    const uint32_t sb = sa + A_TILE_BYTES;
+                    const uint64_t ad = ptx::make_smem_desc(sa, a_lbo, 1024u);
+                    const uint64_t bd = ptx::make_smem_desc(sb, b_lbo, 1024u);
+#pragma unroll
+                    for (uint32_t k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                        ptx::umma_f16<1>(d_tmem, ad + k * a_kstep, bd + k * b_kstep, p.idesc,
+                                         (kb > c.kb0 || k > 0u) ? 1u : 0u);
+                    }
+                    ptx::umma_commit(ptx::smem_u32(&s_empty[stage])); // slot free when MMAs retire
+                    if (++stage == stages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                ptx::umma_commit(ptx::smem_u32(&s_tfull[buf])); // accumulator complete
+            }
+            // All MMAs must have retired before TMEM is released and shared memory goes away.
+            ptx::umma_commit(ptx::smem_u32(&s_drain));
+            const uint64_t t0 = ptx::global_timer_ns();
+            while (!ptx::mbar_try_wait(ptx::smem_u32(&s_drain), 0u)) {
+                if (ptx::global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+                    atomicOr(p.status, ST_DRAIN_WAIT);
+                    break;
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue
+        const uint32_t q    = warp & 3u; // TMEM lane quarter this warp may read
+        const uint32_t stg  = epi + q * 2u * EPI_BUF_BYTES;
+        uint32_t       it   = 0, nstore = 0;
+        bool           ok   = true;
+        for (uint32_t w = blockIdx.x; ok && w < p.num_work; w += gridDim.x, ++it) {
+            const WorkCoord c      = decode_work(p, w, BN);
+            const uint32_t  buf    = it & 1u;
+            const uint32_t  aphase = (it >> 1) & 1u;
+            ok = bounded_wait(ptx::smem_u32(&s_tfull[buf]), aphase, &s_abort, p.status,
+                              ST_EPI_WAIT);
+            ok = __all_sync(0xffffffffu, ok); // warp-uniform: the TMEM loads below are aligned
+            if (!ok) break;
+            ptx::tc_fence_after();
+            const uint32_t row0     = c.m0 + q * 32u;
+            const bool     row_live = row0 < p.M;
+#pragma unroll 1
+            for (int ch = 0; ch < NCHUNK; ++ch) {
+                const uint32_t taddr = tmem_base + ((q * 32u) << 16) + buf * BN + ch * CH;
+                uint32_t       v[32];
+                if constexpr (OUT == OUT_F32) {
+                    ptx::tmem_ld_32x32(taddr, v);
+                    ptx::tmem_ld_wait();
+                } else {
+                    uint32_t lo[32], hi[32];
+                    ptx::tmem_ld_32x32(taddr, lo);
+                    ptx::tmem_ld_32x32(taddr + 32u, hi);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        v[j]      = pack2<OUT>(lo[2 * j], lo[2 * j + 1]);
+                        v[16 + j] = pack2<OUT>(hi[2 * j], hi[2 * j + 1]);
+                    }
+                }
+                if (ch == NCHUNK - 1) {
+                    // Accumulator fully read: hand it back to the MMA issuer.
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&s_tempty[buf]));
+                }
+                const uint32_t col0 = c.n0 + ch * CH;
+                if (row_live && col0 < p.N) {
+                    const uint32_t sbuf = stg + (nstore & 1u) * EPI_BUF_BYTES;
+                    // The store that last used this buffer (two stores ago) must have read it.
+                    if (lane == 0) ptx::tma_store_wait_read<1>();
+                    __syncwarp();
+                    const uint32_t rowaddr = sbuf + lane * 128u;
+#pragma unroll
+                    for (uint32_t j = 0; j < 8; ++j) {
+                        st_shared_v4(rowaddr + ((j ^ (lane & 7u)) << 4), v[4 * j], v[4 * j + 1],
+                                     v[4 * j + 2], v[4 * j + 3]);
+                    }
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::tma_store_3d(&tmD, sbuf, col0, row0, c.z_out);
+                        ptx::tma_store_commit();
+                    }
+                    ++nstore;
+                }
+            }
+        }
+        if (lane == 0) ptx::tma_store_wait_all<0>();
+    }
+
+    // ---------------------------------------------------------------------- tail
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        __syncwarp();
+        ptx::tmem_dealloc<1>(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Split-K reduction: out[z][i] = convert(sum_s ws[z][s][i]), s ascending (deterministic).
+// `ws` holds batch * split_k partial matrices of `mn` f32 elements each.
+// ---------------------------------------------------------------------------------------------
+template <int OUT>
+__global__ void __launch_bounds__(256)
+    splitk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ out, uint64_t mn,
+                         uint32_t split_k, uint32_t batch)
+{
+    const uint64_t total4 = (mn * batch) >> 2; // mn is a multiple of 4
+    const uint64_t mn4    = mn >> 2;
+    for (uint64_t i = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x; i < total4;
+         i += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        const uint64_t z   = i / mn4;
+        const uint64_t e   = i - z * mn4;
+        const float4*  src = reinterpret_cast<const float4*>(ws) + z * split_k * mn4 + e;
+        float4         acc = __ldg(src);
+        for (uint32_t s = 1; s < split_k; ++s) {
+            const float4 t = __ldg(src + s * mn4);
+            acc.x += t.x;
+            acc.y += t.y;
+            acc.z += t.z;
+            acc.w += t.w;
+        }
+        if constexpr (OUT == OUT_F32) {
+            reinterpret_cast<float4*>(out)[i] = acc;
+        } else if constexpr (OUT == OUT_F16) {
+            const __half2 a = __floats2half2_rn(acc.x, acc.y);
+            const __half2 b = __floats2half2_rn(acc.z, acc.w);
+            uint2         u;
+            u.x = *reinterpret_cast<const uint32_t*>(&a);
+            u.y = *reinterpret_cast<const uint32_t*>(&b);
+            reinterpret_cast<uint2*>(out)[i] = u;
+        } else {
+            const __nv_bfloat162 a = __floats2bfloat162_rn(acc.x, acc.y);
+            const __nv_bfloat162 b = __floats2bfloat162_rn(acc.z, acc.w);
+            uint2                u;
+            u.x = *reinterpret_cast<const uint32_t*>(&a);
+            u.y = *reinterpret_cast<const uint32_t*>(&b);
+            reinterpret_cast<uint2*>(out)[i] = u;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// CUDA-core GEMM with arbitrary element strides, f32 accumulation in ascending k.  Only used
+// for shapes whose contiguous extents are not multiples of 16 bytes (TMA cannot address
+// them); correctness path, not a performance path.
+// ---------------------------------------------------------------------------------------------
+template <class TIn, class TOut>
+__global__ void __launch_bounds__(256)
+    gemm_generic_kernel(TOut* __restrict__ C, const TIn* __restrict__ A,
+                        const TIn* __restrict__ B, uint32_t M, uint32_t N, uint32_t K,
+                        uint64_t a_sm, uint64_t a_sk, uint64_t b_sk, uint64_t b_sn, uint64_t c_sm,
+                        uint64_t c_sn, uint64_t a_sb, uint64_t b_sb, uint64_t c_sb)
+{
+    __shared__ float sA[16][17];
+    __shared__ float sB[16][17];
+    const uint32_t   tx = threadIdx.x & 15u, ty = threadIdx.x >> 4;
+    const uint32_t   i = blockIdx.y * 16u + ty, j = blockIdx.x * 16u + tx;
+    const TIn*       Ab  = A + blockIdx.z * a_sb;
+    const TIn*       Bb  = B + blockIdx.z * b_sb;
+    float            acc = 0.f;
+    for (uint32_t k0 = 0; k0 < K; k0 += 16u) {
+        const uint32_t ka = k0 + tx, kb = k0 + ty;
+        sA[ty][tx] = (i < M && ka < K) ? static_cast<float>(Ab[i * a_sm + ka * a_sk]) : 0.f;
+        sB[ty][tx] = (kb < K && j < N) ? static_cast<float>(Bb[kb * b_sk + j * b_sn]) : 0.f;
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 16; ++k) acc += sA[ty][k] * sB[k][tx];
+        __syncthreads();
+    }
+    if (i < M && j < N) C[blockIdx.z * c_sb + i * c_sm + j * c_sn] = static_cast<TOut>(acc);
+}
+
+} // namespace b200

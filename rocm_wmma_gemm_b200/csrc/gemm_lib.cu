@@ -1,0 +1,677 @@
+// Host side of the B200 GEMM library: argument validation, the layout -> kernel-view mapping,
+// tuned-config selection, TMA descriptor construction, kernel launch, and the C ABI declared
+// in include/b200_gemm.h.  Replaces the reference's host path
+//   rocm_wmma_gemm/src/gemm.cpp:8-53, :207-250           (gemm<> and the C dispatchers)
+//   rocm_wmma_gemm/include/rocm_wmma_gemm/kernel_launcher.hpp:45-131   (index math + launch)
+//   generated config_generated.hpp (rocm_wmma_gemm/config/generate_config.py:94-303)
+// There is no CPU fallback: without a CUDA device every compute entry point fails.
+#include "../../include/b200_gemm.h"
+#include "gemm_kernels.cuh"
+
+#include <algorithm>
+#include <atomic>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <limits>
+#include <mutex>
+
+namespace b200 {
+
+// ------------------------------------------------------------------------------------------
+// Errors
+// ------------------------------------------------------------------------------------------
+static thread_local int  t_last_status = B200_GEMM_OK;
+static thread_local char t_last_error[512] = "";
+
+static int fail(int status, const char* fmt, ...)
+{
+    t_last_status = status;
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_last_error, sizeof(t_last_error), fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+#define CUDA_TRY(expr)                                                                         \
+    do {                                                                                       \
+        cudaError_t e_ = (expr);                                                               \
+        if (e_ != cudaSuccess)                                                                 \
+            return fail(B200_GEMM_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e_));   \
+    } while (0)
+
+static std::atomic<unsigned long long> g_launches{0};
+
+// ------------------------------------------------------------------------------------------
+// Tuned configuration table (generated from config/gemm_config_sm100_*.json)
+// ------------------------------------------------------------------------------------------
+struct ConfigEntry {
+    uint32_t m, n, k;
+    uint8_t  type_group; // 0: 16-bit output, 1: f32 output
+    uint8_t  la, lb, lc; // 0 row-major, 1 column-major
+    uint16_t cfg;        // index into k_configs
+};
+
+#include "config_table.inc"
+
+static constexpr int k_num_configs = sizeof(k_configs) / sizeof(k_configs[0]);
+static constexpr int k_num_entries = sizeof(k_entries) / sizeof(k_entries[0]) - 1; // sentinel
+
+static bool entry_less(const ConfigEntry& a, const ConfigEntry& b)
+{
+    if (a.m != b.m) return a.m < b.m;
+    if (a.n != b.n) return a.n < b.n;
+    if (a.k != b.k) return a.k < b.k;
+    if (a.type_group != b.type_group) return a.type_group < b.type_group;
+    if (a.la != b.la) return a.la < b.la;
+    if (a.lb != b.lb) return a.lb < b.lb;
+    return a.lc < b.lc;
+}
+
+// Exact lookup by binary search over the sorted entry list; -1 when absent.
+static int search_exact(size_t m, size_t n, size_t k, int tg, int la, int lb, int lc)
+{
+    if (m > UINT32_MAX || n > UINT32_MAX || k > UINT32_MAX) return -1;
+    const ConfigEntry key{(uint32_t)m, (uint32_t)n, (uint32_t)k, (uint8_t)tg,
+                          (uint8_t)la, (uint8_t)lb, (uint8_t)lc, 0};
+    int lo = 0, hi = k_num_entries;
+    while (lo < hi) {
+        const int mid = (lo + hi) / 2;
+        if (entry_less(k_entries[mid], key)) lo = mid + 1;
+        else hi = mid;
+    }
+    if (lo < k_num_entries && !entry_less(key, k_entries[lo]) && !entry_less(k_entries[lo], key))
+        return k_entries[lo].cfg;
+    return -1;
+}
+
+// Closest entry of one type group within the same layout triple: nearest K first, then the
+// nearest (M, N) in the Euclidean sense among entries with that K; -1 when the group has no
+// entry for the layout triple.
+static int search_closest(size_t m, size_t n, size_t k, int tg, int la, int lb, int lc)
+{
+    bool     found      = false;
+    uint64_t best_kdiff = std::numeric_limits<uint64_t>::max();
+    uint32_t closest_k  = 0;
+    for (int i = 0; i < k_num_entries; ++i) {
+        const ConfigEntry& e = k_entries[i];
+        if (e.type_group != tg || e.la != la || e.lb != lb || e.lc != lc) continue;
+        found               = true;
+        const uint64_t diff = e.k > k ? e.k - k : k - e.k;
+        if (diff < best_kdiff) {
+            best_kdiff = diff;
+            closest_k  = e.k;
+        }
+    }
+    if (!found) return -1;
+    double best_d = std::numeric_limits<double>::max();
+    int    best   = -1;
+    for (int i = 0; i < k_num_entries; ++i) {
+        const ConfigEntry& e = k_entries[i];
+        if (e.type_group != tg || e.k != closest_k || e.la != la || e.lb != lb || e.lc != lc)
+            continue;
+        const double dm = (double)m - (double)e.m, dn = (double)n - (double)e.n;
+        const double d  = dm * dm + dn * dn;
+        if (d < best_d) {
+            best_d = d;
+            best   = e.cfg;
+        }
+    }
+    return best;
+}
+
+// Selection order of the reference's find_best_config
+// (rocm_wmma_gemm/config/generate_config.py:238-271): exact in the requested type group,
+// exact in group 0, closest in the requested group, closest in group 0, default.
+static int find_best_config(size_t m, size_t n, size_t k, int tg, int la, int lb, int lc)
+{
+    int r = search_exact(m, n, k, tg, la, lb, lc);
+    if (r >= 0) return r;
+    if (tg != 0) {
+        r = search_exact(m, n, k, 0, la, lb, lc);
+        if (r >= 0) return r;
+    }
+    r = search_closest(m, n, k, tg, la, lb, lc);
+    if (r < 0 && tg != 0) r = search_closest(m, n, k, 0, la, lb, lc);
+    if (r < 0) r = k_default_config;
+    return r;
+}
+
+// ------------------------------------------------------------------------------------------
+// Per-device context
+// ------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct DeviceCtx {
+    bool          ready    = false;
+    int           sm_count = 0;
+    unsigned int* d_status = nullptr;
+    // host-buffer path
+    cudaStream_t h_stream = nullptr;
+    void*        h_buf[3] = {nullptr, nullptr, nullptr};
+    size_t       h_cap[3] = {0, 0, 0};
+};
+
+static constexpr int k_max_devices = 64;
+static DeviceCtx     g_ctx[k_max_devices];
+static std::mutex    g_mutex;
+static EncodeTiledFn g_encode = nullptr;
+
+template <int BN, int OUT>
+static cudaError_t set_smem_attr()
+{
+    return cudaFuncSetAttribute(gemm_umma_kernel<BN, OUT>,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)gemm_smem_bytes(BN, BN == 256 ? 4 : (BN == 128 ? 6 : 8)));
+}
+
+static int get_ctx(DeviceCtx** out)
+{
+    int         dev = -1;
+    cudaError_t e   = cudaGetDevice(&dev);
+    if (e != cudaSuccess)
+        return fail(B200_GEMM_ERR_NO_DEVICE, "no CUDA device: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= k_max_devices)
+        return fail(B200_GEMM_ERR_NO_DEVICE, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceCtx&                  c = g_ctx[dev];
+    if (!c.ready) {
+        cudaDeviceProp prop;
+        CUDA_TRY(cudaGetDeviceProperties(&prop, dev));
+        if (prop.major != 10)
+            return fail(B200_GEMM_ERR_NO_DEVICE,
+                        "device %d is sm_%d%d; this library is built for sm_100a only", dev,
+                        prop.major, prop.minor);
+        c.sm_count = prop.multiProcessorCount;
+        if (!g_encode) {
+            void*                           fn = nullptr;
+            cudaDriverEntryPointQueryResult qr;
+            CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr));
+            if (!fn || qr != cudaDriverEntryPointSuccess)
+                return fail(B200_GEMM_ERR_CUDA, "cuTensorMapEncodeTiled not available");
+            g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+        }
+        CUDA_TRY(cudaMalloc(&c.d_status, sizeof(unsigned int)));
+        CUDA_TRY(cudaMemset(c.d_status, 0, sizeof(unsigned int)));
+        CUDA_TRY((set_smem_attr<64, OUT_F32>()));
+        CUDA_TRY((set_smem_attr<64, OUT_F16>()));
+        CUDA_TRY((set_smem_attr<64, OUT_BF16>()));
+        CUDA_TRY((set_smem_attr<128, OUT_F32>()));
+        CUDA_TRY((set_smem_attr<128, OUT_F16>()));
+        CUDA_TRY((set_smem_attr<128, OUT_BF16>()));
+        CUDA_TRY((set_smem_attr<256, OUT_F32>()));
+        CUDA_TRY((set_smem_attr<256, OUT_F16>()));
+        CUDA_TRY((set_smem_attr<256, OUT_BF16>()));
+        c.ready = true;
+    }
+    *out = &c;
+    return B200_GEMM_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// Problem description
+// ------------------------------------------------------------------------------------------
+struct Problem {
+    int         types; // b200_gemm_types
+    void*       C;
+    const void* A;
+    const void* B;
+    size_t      M, N, K, batch;
+    int         lc, la, lb;
+};
+
+// Kernel view: D (Mk x Nk row-major) = A' (Mk x K) * B' (K x Nk).
+struct View {
+    const void* a;
+    const void* b;
+    void*       d;
+    uint32_t    M, N, K;
+    bool        a_mn, b_mn;
+};
+
+static View make_view(const Problem& p)
+{
+    View v;
+    v.K = (uint32_t)p.K;
+    if (p.lc == 0) {
+        v.a    = p.A;
+        v.b    = p.B;
+        v.M    = (uint32_t)p.M;
+        v.N    = (uint32_t)p.N;
+        v.a_mn = (p.la == 1); // column-major A: M contiguous
+        v.b_mn = (p.lb == 0); // row-major B: N contiguous
+    } else {
+        // Column-major C (M x N) is the row-major C^T (N x M) = B^T * A^T.
+        v.a    = p.B;
+        v.b    = p.A;
+        v.M    = (uint32_t)p.N;
+        v.N    = (uint32_t)p.M;
+        v.a_mn = (p.lb == 0); // B^T of a row-major B has its "M" (= N) extent contiguous
+        v.b_mn = (p.la == 1); // A^T of a column-major A has its "N" (= M) extent contiguous
+    }
+    v.d = p.C;
+    return v;
+}
+
+static inline bool out_is_f32(int types) { return types == B200_GEMM_F32_F16 || types == B200_GEMM_F32_BF16; }
+static inline bool in_is_bf16(int types) { return types == B200_GEMM_BF16_BF16 || types == B200_GEMM_F32_BF16; }
+static inline int  out_kind(int types)
+{
+    return out_is_f32(types) ? OUT_F32 : (types == B200_GEMM_F16_F16 ? OUT_F16 : OUT_BF16);
+}
+
+static int validate(const Problem& p)
+{
+    if (p.types < 0 || p.types > 3) return fail(B200_GEMM_ERR_BAD_CONFIG, "unknown type pair %d", p.types);
+    if ((p.lc | p.la | p.lb) & ~1)
+        return fail(B200_GEMM_ERR_BAD_LAYOUT, "layout ints must be 0 (row-major) or 1 (column-major): c=%d a=%d b=%d", p.lc, p.la, p.lb);
+    const size_t lim = 0x7fffffffull;
+    if (p.M > lim || p.N > lim || p.K > lim || p.batch > 65535 * 1024ull)
+        return fail(B200_GEMM_ERR_BAD_SIZE, "dimension out of range: M=%zu N=%zu K=%zu batch=%zu", p.M, p.N, p.K, p.batch);
+    if (p.batch == 0) return fail(B200_GEMM_ERR_BAD_SIZE, "batch_count must be >= 1");
+    if (p.M == 0 || p.N == 0) return B200_GEMM_OK; // empty C: nothing to do
+    if (!p.C) return fail(B200_GEMM_ERR_NULL_POINTER, "C is NULL");
+    if (p.K != 0 && (!p.A || !p.B)) return fail(B200_GEMM_ERR_NULL_POINTER, "A or B is NULL");
+    const size_t out_sz = out_is_f32(p.types) ? 4 : 2;
+    if ((reinterpret_cast<uintptr_t>(p.C) % out_sz) || (reinterpret_cast<uintptr_t>(p.A) % 2) ||
+        (reinterpret_cast<uintptr_t>(p.B) % 2))
+        return fail(B200_GEMM_ERR_MISALIGNED, "a pointer is not aligned to its element size");
+    return B200_GEMM_OK;
+}
+
+// Can TMA address this view?  Needs 16-byte aligned bases and 16-byte multiples for every
+// non-innermost stride.
+static bool tma_ok(const Problem& p, const View& v)
+{
+    const size_t out_sz = out_is_f32(p.types) ? 4 : 2;
+    if (reinterpret_cast<uintptr_t>(v.a) % 16 || reinterpret_cast<uintptr_t>(v.b) % 16 ||
+        reinterpret_cast<uintptr_t>(v.d) % 16)
+        return false;
+    const uint32_t a_inner = v.a_mn ? v.M : v.K;
+    const uint32_t b_inner = v.b_mn ? v.N : v.K;
+    if (a_inner % 8 || b_inner % 8) return false;
+    if (p.batch > 1 && (((size_t)v.M * v.K) % 8 || ((size_t)v.N * v.K) % 8)) return false;
+    if ((v.N * out_sz) % 16) return false;
+    if (p.batch > 1 && (((size_t)v.M * v.N * out_sz) % 16)) return false;
+    return true;
+}
+
+// ------------------------------------------------------------------------------------------
+// Configuration handling
+// ------------------------------------------------------------------------------------------
+static int max_stages_for(int tile_n) { return tile_n == 256 ? 4 : (tile_n == 128 ? 6 : 8); }
+
+static int check_config(const b200_gemm_config& c)
+{
+    if (c.tile_m != 128) return fail(B200_GEMM_ERR_BAD_CONFIG, "tile_m %d not compiled (128 only)", c.tile_m);
+    if (c.tile_n != 64 && c.tile_n != 128 && c.tile_n != 256)
+        return fail(B200_GEMM_ERR_BAD_CONFIG, "tile_n %d not compiled (64, 128, 256)", c.tile_n);
+    if (c.cluster != 1) return fail(B200_GEMM_ERR_BAD_CONFIG, "cluster %d not compiled (1 only)", c.cluster);
+    if (c.stages < 2 || c.stages > MAX_STAGES) return fail(B200_GEMM_ERR_BAD_CONFIG, "stages %d outside 2..%d", c.stages, MAX_STAGES);
+    if (c.split_k < 1 || c.split_k > 64) return fail(B200_GEMM_ERR_BAD_CONFIG, "split_k %d outside 1..64", c.split_k);
+    if (c.raster < 0 || c.raster > 64) return fail(B200_GEMM_ERR_BAD_CONFIG, "raster %d outside 0..64", c.raster);
+    return B200_GEMM_OK;
+}
+
+// Fit a (table or caller) config to one problem: clamp the ring depth to what shared memory
+// holds and give every K partition at least one k-block.
+static void legalize(b200_gemm_config& c, const View& v, uint32_t* kb_per_split)
+{
+    const int ms = max_stages_for(c.tile_n);
+    if (c.stages > ms) c.stages = ms;
+    const uint32_t k_blocks = (v.K + BLOCK_K - 1) / BLOCK_K;
+    uint32_t       split    = (uint32_t)c.split_k;
+    if (split > k_blocks) split = k_blocks;
+    if (split < 1) split = 1;
+    const uint32_t per = (k_blocks + split - 1) / split;
+    split              = (k_blocks + per - 1) / per;
+    c.split_k          = (int)split;
+    *kb_per_split      = per;
+}
+
+static b200_gemm_config resolve_config(const Problem& p, const b200_gemm_config* user, int* idx)
+{
+    if (user) {
+        if (idx) *idx = -1;
+        return *user;
+    }
+    const int i = find_best_config(p.M, p.N, p.K, out_is_f32(p.types) ? 1 : 0, p.la, p.lb, p.lc);
+    if (idx) *idx = i;
+    return k_configs[i];
+}
+
+// ------------------------------------------------------------------------------------------
+// TMA descriptors
+// ------------------------------------------------------------------------------------------
+static int encode_map(CUtensorMap* tm, CUtensorMapDataType dt, size_t esz, const void* base,
+                      uint64_t d0, uint64_t d1, uint64_t d2, uint32_t b0, uint32_t b1)
+{
+    const cuuint64_t dims[3]    = {d0, d1, d2};
+    const cuuint64_t strides[2] = {d0 * esz, d0 * d1 * esz};
+    const cuuint32_t box[3]     = {b0, b1, 1};
+    const cuuint32_t estr[3]    = {1, 1, 1};
+    const CUresult   r = g_encode(tm, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
+                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(B200_GEMM_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) dims=%llu,%llu,%llu box=%u,%u", (int)r,
+                    (unsigned long long)d0, (unsigned long long)d1, (unsigned long long)d2, b0, b1);
+    return B200_GEMM_OK;
+}
+
+// Operand with MN extent `rows`: K-major -> [batch][rows][K], box 64 x box_rows;
+// MN-major -> [batch][K][rows], box 64 (MN) x 64 (K).
+static int encode_operand(CUtensorMap* tm, bool bf16, const void* base, uint32_t rows, uint32_t K,
+                          size_t batch, bool mn_major, uint32_t box_rows)
+{
+    const CUtensorMapDataType dt = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    if (!mn_major) return encode_map(tm, dt, 2, base, K, rows, batch, BLOCK_K, box_rows);
+    return encode_map(tm, dt, 2, base, rows, K, batch, 64, BLOCK_K);
+}
+
+// ------------------------------------------------------------------------------------------
+// Launch
+// ------------------------------------------------------------------------------------------
+template <int BN>
+static cudaError_t launch_bn(int out, dim3 grid, uint32_t smem, cudaStream_t s, const CUtensorMap& a,
+                             const CUtensorMap& b, const CUtensorMap& d, const GemmParams& gp)
+{
+    switch (out) {
+        case OUT_F32: gemm_umma_kernel<BN, OUT_F32><<<grid, GEMM_THREADS, smem, s>>>(a, b, d, gp); break;
+        case OUT_F16: gemm_umma_kernel<BN, OUT_F16><<<grid, GEMM_THREADS, smem, s>>>(a, b, d, gp); break;
+        default: gemm_umma_kernel<BN, OUT_BF16><<<grid, GEMM_THREADS, smem, s>>>(a, b, d, gp); break;
+    }
+    return cudaGetLastError();
+}
+
+template <class TIn, class TOut>
+static cudaError_t launch_generic(const Problem& p, cudaStream_t s)
+{
+    // Element strides of the caller's (not the kernel-view) matrices.
+    const uint64_t a_sm = p.la == 0 ? p.K : 1, a_sk = p.la == 0 ? 1 : p.M;
+    const uint64_t b_sk = p.lb == 0 ? p.N : 1, b_sn = p.lb == 0 ? 1 : p.K;
+    const uint64_t c_sm = p.lc == 0 ? p.N : 1, c_sn = p.lc == 0 ? 1 : p.M;
+    for (size_t b0 = 0; b0 < p.batch; b0 += 65535) {
+        const unsigned nb = (unsigned)std::min<size_t>(65535, p.batch - b0);
+        dim3           grid((unsigned)((p.N + 15) / 16), (unsigned)((p.M + 15) / 16), nb);
+        if (grid.y > 65535) return cudaErrorInvalidConfiguration;
+        gemm_generic_kernel<TIn, TOut><<<grid, 256, 0, s>>>(
+            static_cast<TOut*>(p.C) + b0 * p.M * p.N, static_cast<const TIn*>(p.A) + b0 * p.M * p.K,
+            static_cast<const TIn*>(p.B) + b0 * p.K * p.N, (uint32_t)p.M, (uint32_t)p.N, (uint32_t)p.K, a_sm,
+            a_sk, b_sk, b_sn, c_sm, c_sn, p.M * p.K, p.K * p.N, p.M * p.N);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+    }
+    return cudaGetLastError();
+}
+
+static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_config* user_cfg)
+{
+    int st = validate(p);
+    if (st != B200_GEMM_OK) return st;
+    if (p.M == 0 || p.N == 0) return B200_GEMM_OK;
+
+    DeviceCtx* ctx = nullptr;
+    st             = get_ctx(&ctx);
+    if (st != B200_GEMM_OK) return st;
+
+    const size_t out_sz = out_is_f32(p.types) ? 4 : 2;
+    if (p.K == 0) { // empty sum: C = 0
+        CUDA_TRY(cudaMemsetAsync(p.C, 0, p.M * p.N * p.batch * out_sz, stream));
+        return B200_GEMM_OK;
+    }
+
+    const View v = make_view(p);
+    if (!tma_ok(p, v)) {
+        cudaError_t e;
+        switch (p.types) {
+            case B200_GEMM_F16_F16: e = launch_generic<__half, __half>(p, stream); break;
+            case B200_GEMM_F32_F16: e = launch_generic<__half, float>(p, stream); break;
+            case B200_GEMM_BF16_BF16: e = launch_generic<__nv_bfloat16, __nv_bfloat16>(p, stream); break;
+            default: e = launch_generic<__nv_bfloat16, float>(p, stream); break;
+        }
+        if (e != cudaSuccess) return fail(B200_GEMM_ERR_CUDA, "generic kernel launch failed: %s", cudaGetErrorString(e));
+        return B200_GEMM_OK;
+    }
+
+    b200_gemm_config cfg = resolve_config(p, user_cfg, nullptr);
+    st                   = check_config(cfg);
+    if (st != B200_GEMM_OK) return st;
+    uint32_t kb_per_split = 0;
+    legalize(cfg, v, &kb_per_split);
+
+    const int      bn   = cfg.tile_n;
+    const int      out  = out_kind(p.types);
+    const bool     bf16 = in_is_bf16(p.types);
+    const uint32_t split = (uint32_t)cfg.split_k;
+
+    GemmParams gp;
+    gp.M            = v.M;
+    gp.N            = v.N;
+    gp.K            = v.K;
+    gp.batch        = (uint32_t)p.batch;
+    gp.m_tiles      = (v.M + BLOCK_M - 1) / BLOCK_M;
+    gp.n_tiles      = (v.N + bn - 1) / bn;
+    gp.k_blocks     = (v.K + BLOCK_K - 1) / BLOCK_K;
+    gp.split_k      = split;
+    gp.kb_per_split = kb_per_split;
+    gp.group_m      = (uint32_t)cfg.raster;
+    const uint64_t work = (uint64_t)gp.batch * split * gp.m_tiles * gp.n_tiles;
+    if (work > 0x7fffffffull) return fail(B200_GEMM_ERR_BAD_SIZE, "too many tiles (%llu)", (unsigned long long)work);
+    gp.num_work   = (uint32_t)work;
+    gp.a_mn_major = v.a_mn ? 1u : 0u;
+    gp.b_mn_major = v.b_mn ? 1u : 0u;
+    // tcgen05 instruction descriptor, kind::f16: [4,6) D format (1 = f32); [7,10) A format and
+    // [10,13) B format (0 = f16, 1 = bf16); bit 15 / 16: A / B is MN-major; [17,23) N >> 3;
+    // [24,29) M >> 4.
+    gp.idesc = (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | (gp.a_mn_major << 15) |
+               (gp.b_mn_major << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BLOCK_M >> 4) << 24);
+    gp.stages = (uint32_t)cfg.stages;
+    gp.status = ctx->d_status;
+
+    // Split-K partials go to a stream-ordered f32 workspace laid out [batch][split][Mk][Nk].
+    float*       ws       = nullptr;
+    const size_t ws_bytes = split > 1 ? (size_t)p.batch * split * v.M * v.N * sizeof(float) : 0;
+    if (split > 1) {
+        if (v.N % 4) return fail(B200_GEMM_ERR_BAD_CONFIG, "split_k needs N %% 4 == 0 in the kernel view");
+        CUDA_TRY(cudaMallocAsync(reinterpret_cast<void**>(&ws), ws_bytes, stream));
+    }
+
+    CUtensorMap tmA, tmB, tmD;
+    st = encode_operand(&tmA, bf16, v.a, v.M, v.K, p.batch, v.a_mn, BLOCK_M);
+    if (st == B200_GEMM_OK) st = encode_operand(&tmB, bf16, v.b, v.N, v.K, p.batch, v.b_mn, (uint32_t)bn);
+    if (st == B200_GEMM_OK) {
+        if (split > 1)
+            st = encode_map(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ws, v.N, v.M, (uint64_t)p.batch * split, 32, 32);
+        else if (out == OUT_F32)
+            st = encode_map(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, v.d, v.N, v.M, p.batch, 32, 32);
+        else
+            st = encode_map(&tmD, out == OUT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                            v.d, v.N, v.M, p.batch, 64, 32);
+    }
+    if (st != B200_GEMM_OK) {
+        if (ws) cudaFreeAsync(ws, stream);
+        return st;
+    }
+
+    const uint32_t smem     = gemm_smem_bytes(bn, cfg.stages);
+    const dim3     grid(std::min<uint32_t>(gp.num_work, (uint32_t)ctx->sm_count));
+    const int      kern_out = split > 1 ? OUT_F32 : out;
+    cudaError_t    e;
+    switch (bn) {
+        case 64: e = launch_bn<64>(kern_out, grid, smem, stream, tmA, tmB, tmD, gp); break;
+        case 128: e = launch_bn<128>(kern_out, grid, smem, stream, tmA, tmB, tmD, gp); break;
+        default: e = launch_bn<256>(kern_out, grid, smem, stream, tmA, tmB, tmD, gp); break;
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (e != cudaSuccess) {
+        if (ws) cudaFreeAsync(ws, stream);
+        return fail(B200_GEMM_ERR_CUDA, "GEMM kernel launch failed: %s (tile_n=%d stages=%d smem=%u)", cudaGetErrorString(e), bn,
+                    cfg.stages, smem);
+    }
+
+    if (split > 1) {
+        const uint64_t mn     = (uint64_t)v.M * v.N;
+        const uint64_t total4 = mn * p.batch / 4;
+        const unsigned blocks = (unsigned)std::min<uint64_t>((total4 + 255) / 256, (uint64_t)ctx->sm_count * 8);
+        switch (out) {
+            case OUT_F32: splitk_reduce_kernel<OUT_F32><<<blocks, 256, 0, stream>>>(ws, v.d, mn, split, (uint32_t)p.batch); break;
+            case OUT_F16: splitk_reduce_kernel<OUT_F16><<<blocks, 256, 0, stream>>>(ws, v.d, mn, split, (uint32_t)p.batch); break;
+            default: splitk_reduce_kernel<OUT_BF16><<<blocks, 256, 0, stream>>>(ws, v.d, mn, split, (uint32_t)p.batch); break;
+        }
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        e = cudaGetLastError();
+        cudaFreeAsync(ws, stream);
+        if (e != cudaSuccess) return fail(B200_GEMM_ERR_CUDA, "split-K reduce launch failed: %s", cudaGetErrorString(e));
+    }
+    return B200_GEMM_OK;
+}
+
+static int run_from_abi(int types, void* C, const void* A, const void* B, size_t M, size_t N, size_t K,
+                        size_t batch, int lc, int la, int lb, void* stream, const b200_gemm_config* cfg)
+{
+    t_last_status = B200_GEMM_OK;
+    try {
+        const Problem      p{types, C, A, B, M, N, K, batch, lc, la, lb};
+        const cudaStream_t s = stream ? *static_cast<cudaStream_t*>(stream) : nullptr;
+        return run_gemm(p, s, cfg);
+    } catch (const std::exception& ex) {
+        return fail(B200_GEMM_ERR_CUDA, "exception: %s", ex.what());
+    } catch (...) {
+        return fail(B200_GEMM_ERR_CUDA, "unknown exception");
+    }
+}
+
+} // namespace b200
+
+// ==============================================================================================
+// C ABI
+// ==============================================================================================
+using namespace b200;
+
+#define B200_DEFINE_PAIR(suffix, types)                                                              \
+    extern "C" int b200_gemm_##suffix(void* C, void* A, void* B, size_t M, size_t N, size_t K,       \
+                                      size_t batch_count, int layout_c, int layout_a, int layout_b,  \
+                                      void* stream)                                                  \
+    {                                                                                                \
+        return run_from_abi(types, C, A, B, M, N, K, batch_count, layout_c, layout_a, layout_b,      \
+                            stream, nullptr);                                                        \
+    }                                                                                                \
+    extern "C" void rocm_wmma_gemm_##suffix(void* C, void* A, void* B, size_t M, size_t N, size_t K, \
+                                            size_t batch_count, int layout_c, int layout_a,          \
+                                            int layout_b, void* stream)                              \
+    {                                                                                                \
+        (void)run_from_abi(types, C, A, B, M, N, K, batch_count, layout_c, layout_a, layout_b,       \
+                           stream, nullptr);                                                         \
+    }
+
+B200_DEFINE_PAIR(f16_f16, B200_GEMM_F16_F16)
+B200_DEFINE_PAIR(f32_f16, B200_GEMM_F32_F16)
+B200_DEFINE_PAIR(bf16_bf16, B200_GEMM_BF16_BF16)
+B200_DEFINE_PAIR(f32_bf16, B200_GEMM_F32_BF16)
+
+extern "C" int b200_gemm_ex(int types, void* C, const void* A, const void* B, size_t M, size_t N,
+                            size_t K, size_t batch_count, int layout_c, int layout_a, int layout_b,
+                            void* stream, const b200_gemm_config* cfg)
+{
+    return run_from_abi(types, C, A, B, M, N, K, batch_count, layout_c, layout_a, layout_b, stream, cfg);
+}
+
+extern "C" int b200_gemm_select_config(size_t M, size_t N, size_t K, int types, int layout_c,
+                                       int layout_a, int layout_b, b200_gemm_config* out)
+{
+    if (types < 0 || types > 3) return -fail(B200_GEMM_ERR_BAD_CONFIG, "unknown type pair %d", types);
+    if ((layout_c | layout_a | layout_b) & ~1) return -fail(B200_GEMM_ERR_BAD_LAYOUT, "layout ints must be 0 or 1");
+    const int i = find_best_config(M, N, K, out_is_f32(types) ? 1 : 0, layout_a, layout_b, layout_c);
+    if (out) *out = k_configs[i];
+    return i;
+}
+
+extern "C" size_t b200_gemm_workspace_bytes(int types, size_t M, size_t N, size_t K, size_t batch_count,
+                                            int layout_c, int layout_a, int layout_b,
+                                            const b200_gemm_config* user)
+{
+    const Problem p{types, nullptr, nullptr, nullptr, M, N, K, batch_count, layout_c, layout_a, layout_b};
+    if (types < 0 || types > 3 || ((layout_c | layout_a | layout_b) & ~1) || M == 0 || N == 0 || K == 0) return 0;
+    b200_gemm_config cfg = resolve_config(p, user, nullptr);
+    const View       v   = make_view(p);
+    uint32_t         per = 0;
+    legalize(cfg, v, &per);
+    return cfg.split_k > 1 ? batch_count * cfg.split_k * M * N * sizeof(float) : 0;
+}
+
+extern "C" int b200_gemm_slab(size_t N, int world, int rank, size_t align, size_t* n_begin, size_t* n_count)
+{
+    if (world < 1 || rank < 0 || rank >= world || align == 0 || !n_begin || !n_count)
+        return fail(B200_GEMM_ERR_BAD_SIZE, "bad slab request: world=%d rank=%d align=%zu", world, rank, align);
+    // Slab width: N / world rounded up to a multiple of `align`; trailing ranks may get a
+    // narrower (or empty) slab.
+    const size_t units = (N + align - 1) / align;
+    const size_t per   = ((units + world - 1) / world) * align;
+    const size_t b     = std::min(N, per * (size_t)rank);
+    const size_t e     = std::min(N, b + per);
+    *n_begin           = b;
+    *n_count           = e - b;
+    return B200_GEMM_OK;
+}
+
+extern "C" int b200_gemm_host(int types, void* C, const void* A, const void* B, size_t M, size_t N, size_t K,
+                              size_t batch_count, int layout_c, int layout_a, int layout_b)
+{
+    const Problem p{types, C, A, B, M, N, K, batch_count, layout_c, layout_a, layout_b};
+    int           st = validate(p);
+    if (st != B200_GEMM_OK) return st;
+    if (M == 0 || N == 0) return B200_GEMM_OK;
+    DeviceCtx* ctx = nullptr;
+    st             = get_ctx(&ctx);
+    if (st != B200_GEMM_OK) return st;
+    const size_t out_sz   = out_is_f32(types) ? 4 : 2;
+    const size_t bytes[3] = {M * K * batch_count * 2, K * N * batch_count * 2, M * N * batch_count * out_sz};
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        if (!ctx->h_stream) CUDA_TRY(cudaStreamCreateWithFlags(&ctx->h_stream, cudaStreamNonBlocking));
+        for (int i = 0; i < 3; ++i) {
+            if (ctx->h_cap[i] < bytes[i]) {
+                if (ctx->h_buf[i]) CUDA_TRY(cudaFree(ctx->h_buf[i]));
+                ctx->h_buf[i] = nullptr;
+                ctx->h_cap[i] = 0;
+                CUDA_TRY(cudaMalloc(&ctx->h_buf[i], std::max<size_t>(bytes[i], 256)));
+                ctx->h_cap[i] = std::max<size_t>(bytes[i], 256);
+            }
+        }
+    }
+    cudaStream_t s = ctx->h_stream;
+    if (bytes[0]) CUDA_TRY(cudaMemcpyAsync(ctx->h_buf[0], A, bytes[0], cudaMemcpyHostToDevice, s));
+    if (bytes[1]) CUDA_TRY(cudaMemcpyAsync(ctx->h_buf[1], B, bytes[1], cudaMemcpyHostToDevice, s));
+    const Problem dp{types, ctx->h_buf[2], ctx->h_buf[0], ctx->h_buf[1], M, N, K, batch_count, layout_c, layout_a, layout_b};
+    st = run_gemm(dp, s, nullptr);
+    if (st != B200_GEMM_OK) return st;
+    CUDA_TRY(cudaMemcpyAsync(C, ctx->h_buf[2], bytes[2], cudaMemcpyDeviceToHost, s));
+    CUDA_TRY(cudaStreamSynchronize(s));
+    return B200_GEMM_OK;
+}
+
+extern "C" int b200_gemm_device_status(unsigned int* detail)
+{
+    DeviceCtx* ctx = nullptr;
+    int        st  = get_ctx(&ctx);
+    if (st != B200_GEMM_OK) return st;
+    CUDA_TRY(cudaDeviceSynchronize());
+    unsigned int word = 0;
+    CUDA_TRY(cudaMemcpy(&word, ctx->d_status, sizeof(word), cudaMemcpyDeviceToHost));
+    if (detail) *detail = word;
+    if (word != 0) {
+        CUDA_TRY(cudaMemset(ctx->d_status, 0, sizeof(word)));
+        return fail(B200_GEMM_ERR_DEVICE_WAIT, "a kernel gave up on a bounded wait (status word 0x%x)", word);
+    }
+    return B200_GEMM_OK;
+}
+
+extern "C" int b200_gemm_last_status(void) { return t_last_status; }
+extern "C" const char* b200_gemm_last_error(void) { return t_last_error; }
+extern "C" const char* b200_gemm_version(void) { return "b200_gemm 0.1 (sm_100a)"; }
+extern "C" unsigned long long b200_gemm_launch_count(void) { return g_launches.load(); }

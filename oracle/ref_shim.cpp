@@ -112,6 +112,65 @@ float cosine_one(const void* g, const void* c, size_t M, size_t N, int layout)
 
 } // namespace
 
+// hgemm_cpu on rows [row_begin, row_end) of C, the rows split over `threads` host threads.
+// B is placed in ONE `matrix` object shared by all threads; each thread gathers its own row
+// panel of A and calls the reference's hgemm_cpu on (C panel, A panel, B).  `C_rows` receives
+// the panels as a (row_end - row_begin) x N matrix in layout lc.  Used to time the
+// reference's CPU path on all host cores.
+namespace {
+
+template <class TOut, class TIn, m_layout LC, m_layout LA, m_layout LB>
+void rows_mt(void* C_rows, const void* A, const void* B, size_t M, size_t N, size_t K, size_t row_begin,
+             size_t row_end, int threads)
+{
+    const size_t rows = row_end - row_begin;
+    matrix<TIn, LB> b(K, N);
+    fill_from(b, B);
+    const matrix<TIn, LB>&   bref = b;
+    std::vector<std::thread> pool;
+    for (int t = 0; t < threads; ++t) {
+        const size_t r0 = rows * t / threads, r1 = rows * (t + 1) / threads;
+        if (r1 == r0) continue;
+        pool.emplace_back([=, &bref]() {
+            const size_t     pr = r1 - r0;
+            matrix<TIn, LA>  a(pr, K);
+            matrix<TOut, LC> c(pr, N);
+            const TIn*       src = static_cast<const TIn*>(A);
+            for (size_t i = 0; i < pr; ++i)
+                for (size_t k = 0; k < K; ++k) {
+                    const size_t gi = row_begin + r0 + i;
+                    a(i, k)         = src[LA == m_layout::row_major ? gi * K + k : k * M + gi];
+                }
+            hgemm_cpu(c, a, bref);
+            TOut* dst = static_cast<TOut*>(C_rows);
+            for (size_t i = 0; i < pr; ++i)
+                for (size_t j = 0; j < N; ++j)
+                    dst[LC == m_layout::row_major ? (r0 + i) * N + j : j * rows + (r0 + i)] = c(i, j);
+        });
+    }
+    for (auto& th : pool) th.join();
+}
+
+template <class TOut, class TIn>
+void rows_mt_layouts(void* C, const void* A, const void* B, size_t M, size_t N, size_t K, int lc, int la, int lb,
+                     size_t r0, size_t r1, int threads)
+{
+    constexpr m_layout R = m_layout::row_major, Cm = m_layout::col_major;
+    switch (lc << 2 | la << 1 | lb) {
+        case 0: rows_mt<TOut, TIn, R, R, R>(C, A, B, M, N, K, r0, r1, threads); break;
+        case 1: rows_mt<TOut, TIn, R, R, Cm>(C, A, B, M, N, K, r0, r1, threads); break;
+        case 2: rows_mt<TOut, TIn, R, Cm, R>(C, A, B, M, N, K, r0, r1, threads); break;
+        case 3: rows_mt<TOut, TIn, R, Cm, Cm>(C, A, B, M, N, K, r0, r1, threads); break;
+        case 4: rows_mt<TOut, TIn, Cm, R, R>(C, A, B, M, N, K, r0, r1, threads); break;
+        case 5: rows_mt<TOut, TIn, Cm, R, Cm>(C, A, B, M, N, K, r0, r1, threads); break;
+        case 6: rows_mt<TOut, TIn, Cm, Cm, R>(C, A, B, M, N, K, r0, r1, threads); break;
+        case 7: rows_mt<TOut, TIn, Cm, Cm, Cm>(C, A, B, M, N, K, r0, r1, threads); break;
+        default: break;
+    }
+}
+
+} // namespace
+
 extern "C" {
 
 // init_matrix of test/test.hpp on a rows x cols matrix of f16 (bf16 == 0) or bf16 elements.
@@ -127,46 +186,20 @@ void ref_hgemm(int types, void* C, const void* A, const void* B, size_t M, size_
     gemm_types(types, C, A, B, M, N, K, lc, la, lb);
 }
 
-// hgemm_cpu on rows [row_begin, row_end) of C, the rows split over `threads` host threads,
-// each thread calling the reference function on its own row panel (A panel gathered, B
-// shared).  `C_rows` receives the panel as a (row_end - row_begin) x N matrix in layout lc.
-// Used to time the reference's CPU path on all host cores.
 void ref_hgemm_rows_mt(int types, void* C_rows, const void* A, const void* B, size_t M, size_t N, size_t K, int lc,
                        int la, int lb, size_t row_begin, size_t row_end, int threads)
 {
-    const size_t rows = row_end - row_begin;
-    if (rows == 0) return;
-    threads = std::max(1, std::min<int>(threads, (int)rows));
-    const size_t out_sz = (types == 1 || types == 3) ? 4 : 2;
-    std::vector<std::thread> pool;
-    for (int t = 0; t < threads; ++t) {
-        const size_t r0 = rows * t / threads, r1 = rows * (t + 1) / threads;
-        pool.emplace_back([=]() {
-            const size_t pr = r1 - r0;
-            if (pr == 0) return;
-            // Gather the A panel (pr x K) in layout la.
-            std::vector<uint16_t> ap(pr * K);
-            const uint16_t*       a = static_cast<const uint16_t*>(A);
-            for (size_t i = 0; i < pr; ++i)
-                for (size_t k = 0; k < K; ++k) {
-                    const size_t gi  = row_begin + r0 + i;
-                    const size_t src = la == 0 ? gi * K + k : k * M + gi;
-                    const size_t dst = la == 0 ? i * K + k : k * pr + i;
-                    ap[dst]          = a[src];
-                }
-            std::vector<uint8_t> cp(pr * N * out_sz);
-            gemm_types(types, cp.data(), ap.data(), B, pr, N, K, lc, la, lb);
-            // Scatter the C panel into C_rows (rows x N, layout lc).
-            uint8_t* c = static_cast<uint8_t*>(C_rows);
-            for (size_t i = 0; i < pr; ++i)
-                for (size_t j = 0; j < N; ++j) {
-                    const size_t src = lc == 0 ? i * N + j : j * pr + i;
-                    const size_t dst = lc == 0 ? (r0 + i) * N + j : j * rows + (r0 + i);
-                    std::memcpy(c + dst * out_sz, cp.data() + src * out_sz, out_sz);
-                }
-        });
+    if (row_end <= row_begin) return;
+    threads = std::max(1, std::min<int>(threads, (int)(row_end - row_begin)));
+    switch (types) {
+        case 0: rows_mt_layouts<half, half>(C_rows, A, B, M, N, K, lc, la, lb, row_begin, row_end, threads); break;
+        case 1: rows_mt_layouts<float, half>(C_rows, A, B, M, N, K, lc, la, lb, row_begin, row_end, threads); break;
+        case 2:
+            rows_mt_layouts<__hip_bfloat16, __hip_bfloat16>(C_rows, A, B, M, N, K, lc, la, lb, row_begin, row_end, threads);
+            break;
+        case 3: rows_mt_layouts<float, __hip_bfloat16>(C_rows, A, B, M, N, K, lc, la, lb, row_begin, row_end, threads); break;
+        default: break;
     }
-    for (auto& th : pool) th.join();
 }
 
 // calculate_cosine_similarity of test/test.hpp.  kind: 0 f16, 1 f32, 2 bf16.

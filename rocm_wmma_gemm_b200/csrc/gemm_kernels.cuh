@@ -1,6 +1,7 @@
 // Device kernels of the B200 GEMM library.
 //
-//   gemm_umma_kernel   persistent, warp-specialised tcgen05 GEMM, one CTA per 128 x BN tile
+//   gemm_umma_kernel   persistent, warp-specialised tcgen05 GEMM; one CTA per 128 x BN tile or a
+//                      CTA pair per 256 x BN tile
 //   splitk_reduce_kernel   deterministic sum of split-K partials + conversion to the output type
 //   gemm_generic_kernel    CUDA-core GEMM for shapes whose leading dimensions TMA cannot address
 //
@@ -34,7 +35,7 @@ enum : unsigned int {
 struct GemmParams {
     uint32_t M, N, K;      // kernel-view extents
     uint32_t batch;        // batch count
-    uint32_t m_tiles;      // ceil(M / 128)
+    uint32_t m_tiles;      // ceil(M / (128 * cluster))
     uint32_t n_tiles;      // ceil(N / BN)
     uint32_t k_blocks;     // ceil(K / 64)
     uint32_t split_k;      // K partitions (>= 1); every partition owns >= 1 k-block
@@ -58,28 +59,42 @@ constexpr uint32_t EPI_BUF_BYTES  = 32 * 128; // one warp's 32 rows x 128 B
 constexpr uint32_t EPI_BYTES      = 4 * 2 * EPI_BUF_BYTES;
 constexpr uint64_t WAIT_LIMIT_NS  = 2000000000ull; // 2 s per bounded wait
 
-__host__ __device__ constexpr uint32_t stage_bytes(int bn)
+// Bytes of one ring slot in one CTA: A' 128 x 64 plus B' (bn / cluster) x 64.
+__host__ __device__ constexpr uint32_t stage_bytes(int bn, int cluster)
 {
-    return A_TILE_BYTES + static_cast<uint32_t>(bn) * BLOCK_K * 2;
+    return A_TILE_BYTES + static_cast<uint32_t>(bn / cluster) * BLOCK_K * 2;
 }
 
 // Dynamic shared memory a launch needs (1 KiB slack for manual 1024-byte alignment).
-__host__ __device__ constexpr uint32_t gemm_smem_bytes(int bn, int stages)
+__host__ __device__ constexpr uint32_t gemm_smem_bytes(int bn, int cluster, int stages)
 {
-    return static_cast<uint32_t>(stages) * stage_bytes(bn) + EPI_BYTES + 1024;
+    return static_cast<uint32_t>(stages) * stage_bytes(bn, cluster) + EPI_BYTES + 1024;
+}
+
+// Deepest ring that fits the 227 KiB a CTA may use (static barriers included).
+__host__ __device__ constexpr int max_stages(int bn, int cluster)
+{
+    int s = static_cast<int>((232448u - 512u - EPI_BYTES - 1024u) / stage_bytes(bn, cluster));
+    return s > MAX_STAGES ? MAX_STAGES : s;
 }
 
 // Waits for the phase with the given parity; gives up after WAIT_LIMIT_NS or as soon as
-// another role of this CTA has given up.  Returns false on give-up.
+// another role of this CTA has given up.  Returns false on give-up.  CLUSTER_SCOPE selects an
+// acquire at cluster scope (the arrivals come from the peer CTA's threads).
+template <bool CLUSTER_SCOPE = false>
 __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity,
                                              volatile uint32_t* s_abort, unsigned int* status,
                                              unsigned int code)
 {
-    if (ptx::mbar_try_wait(bar, parity)) return true;
+    auto try_wait = [&]() {
+        if constexpr (CLUSTER_SCOPE) return ptx::mbar_try_wait_cluster(bar, parity);
+        else return ptx::mbar_try_wait(bar, parity);
+    };
+    if (try_wait()) return true;
     const uint64_t t0    = ptx::global_timer_ns();
     uint32_t       spins = 0;
     while (true) {
-        if (ptx::mbar_try_wait(bar, parity)) return true;
+        if (try_wait()) return true;
         if ((++spins & 31u) == 0u) {
             if (*s_abort != 0u) return false;
             if (ptx::global_timer_ns() - t0 > WAIT_LIMIT_NS) {
@@ -98,7 +113,7 @@ struct WorkCoord {
     uint32_t kb0, kb1; // k-block range
 };
 
-__device__ __forceinline__ WorkCoord decode_work(const GemmParams& p, uint32_t w, int bn)
+__device__ __forceinline__ WorkCoord decode_work(const GemmParams& p, uint32_t w, int bn, int bm)
 {
     const uint32_t tiles = p.m_tiles * p.n_tiles;
     const uint32_t t     = w % tiles;
@@ -119,7 +134,7 @@ __device__ __forceinline__ WorkCoord decode_work(const GemmParams& p, uint32_t w
         n_idx                    = in_g / gsize;
     }
     WorkCoord c;
-    c.m0    = m_idx * BLOCK_M;
+    c.m0    = m_idx * static_cast<uint32_t>(bm);
     c.n0    = n_idx * static_cast<uint32_t>(bn);
     c.z_in  = b;
     c.z_out = b * p.split_k + split;
@@ -134,6 +149,24 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c),
                  "r"(d)
                  : "memory");
+}
+
+// TMA load whose completion bytes go to `bar`: this CTA's barrier (CL = 1) or a
+// shared::cluster address naming the pair leader's barrier (CL = 2).
+template <int CL>
+__device__ __forceinline__ void tma_load(uint32_t dst, const CUtensorMap* tm, uint32_t bar,
+                                         int32_t c0, int32_t c1, int32_t c2)
+{
+    if constexpr (CL == 2) ptx::tma_load_3d_pair(dst, tm, bar, c0, c1, c2);
+    else ptx::tma_load_3d(dst, tm, bar, c0, c1, c2);
+}
+
+// tcgen05.commit arriving on `bar` of this CTA (CL = 1) or of both CTAs of the pair (CL = 2).
+template <int CL>
+__device__ __forceinline__ void umma_arrive(uint32_t bar)
+{
+    if constexpr (CL == 2) ptx::umma_commit_pair(bar, 0x3);
+    else ptx::umma_commit(bar);
 }
 
 template <int OUT>
@@ -151,33 +184,43 @@ __device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits)
 }
 
 // ---------------------------------------------------------------------------------------------
-// Persistent tcgen05 GEMM, one CTA per 128 x BN output tile.
+// Persistent tcgen05 GEMM.  CL = 1: one CTA per 128 x BN output tile.  CL = 2: a cluster of two
+// CTAs (a "pair", ranks 0 and 1) per 256 x BN tile; each CTA loads its own 128 rows of A' and
+// its own BN/2 columns of B', rank 0 issues one cta_group::2 MMA per K = 16 slice that reads
+// both CTAs' shared memory and writes both CTAs' TMEM (each holds its 128 rows x BN columns).
+// The pair halves the B' bytes each SM has to stage per FLOP.
 //
-//   warp 0 (one lane)  TMA producer: fills a `stages`-deep ring of {A' 128x64, B' BNx64} tiles
-//                      (128-byte swizzle), one mbarrier pair (full/empty) per slot.
-//   warp 1 (one lane)  MMA issuer: 4 x tcgen05.mma (K = 16 each) per slot into one of two
-//                      TMEM accumulators (BN f32 columns each); tcgen05.commit releases the
-//                      slot and, after the last k-block, publishes the accumulator.
+//   warp 0 (one lane)  TMA producer: fills a `stages`-deep ring of {A' 128x64, B' (BN/CL)x64}
+//                      tiles (128-byte swizzle).  Slot s has a `full` barrier (bytes landed;
+//                      for a pair it lives in rank 0 and counts both CTAs' bytes) and an
+//                      `empty` barrier (MMAs that read the slot have retired).
+//   warp 1 (one lane)  MMA issuer (rank 0 only for a pair): 4 x tcgen05.mma per slot into one
+//                      of two TMEM accumulators (BN f32 columns each); tcgen05.commit releases
+//                      the slot and, after the last k-block, publishes the accumulator.
 //   warps 2..5         epilogue: tcgen05.ld 32 lanes x 32 columns, convert, swizzled store to a
 //                      per-warp staging buffer, TMA store of 32 rows x 128 B; the accumulator
 //                      is handed back as soon as its last column chunk is in registers, so the
 //                      epilogue of tile i overlaps the main loop of tile i + 1.
 //
 // Edges: TMA zero-fills out-of-range loads (M, N and K tails) and clips stores.
+// No TMA load here uses cluster multicast.
 // ---------------------------------------------------------------------------------------------
-template <int BN, int OUT>
+template <int BN, int OUT, int CL>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA,
                      const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmD, const GemmParams p)
 {
     static_assert(BN == 64 || BN == 128 || BN == 256, "BN must be 64, 128 or 256");
-    constexpr uint32_t B_TILE_BYTES = BN * BLOCK_K * 2;
+    static_assert(CL == 1 || CL == 2, "cluster size must be 1 or 2");
+    constexpr int      BN_CTA       = BN / CL; // B' rows this CTA stages
+    constexpr uint32_t B_TILE_BYTES = BN_CTA * BLOCK_K * 2;
     constexpr uint32_t STAGE_BYTES  = A_TILE_BYTES + B_TILE_BYTES;
     constexpr uint32_t TMEM_COLS    = 2 * BN; // two accumulators; power of two >= 32
     constexpr int      OUT_BYTES    = (OUT == OUT_F32) ? 4 : 2;
     constexpr int      CH           = 128 / OUT_BYTES; // output columns per 128-byte chunk
     constexpr int      NCHUNK       = BN / CH;
+    static_assert(BN_CTA >= 64, "each CTA stages at least 64 rows of B'");
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t s_full[MAX_STAGES];
@@ -192,6 +235,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     const uint32_t warp   = tid >> 5;
     const uint32_t lane   = tid & 31u;
     const uint32_t stages = p.stages;
+    const uint32_t rank   = (CL == 2) ? ptx::cluster_ctarank() : 0u; // CTA rank in the pair
+    const uint32_t unit   = blockIdx.x / CL;                          // persistent worker index
+    const uint32_t units  = gridDim.x / CL;
 
     const uint32_t ring = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u; // ring of operand tiles
     const uint32_t epi  = ring + stages * STAGE_BYTES;                // epilogue staging
@@ -206,17 +252,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(ptx::smem_u32(&s_tfull[b]), 1);
-            ptx::mbar_init(ptx::smem_u32(&s_tempty[b]), 4);
+            ptx::mbar_init(ptx::smem_u32(&s_tempty[b]), 4 * CL);
         }
         ptx::mbar_init(ptx::smem_u32(&s_drain), 1);
         s_abort = 0u;
         ptx::fence_mbar_init();
     }
     if (warp == 1) {
-        ptx::tmem_alloc<1>(ptx::smem_u32(&s_tmem_base), TMEM_COLS);
+        ptx::tmem_alloc<CL>(ptx::smem_u32(&s_tmem_base), TMEM_COLS);
     }
     ptx::tc_fence_before();
     __syncthreads();
+    if constexpr (CL == 2) { // the peer's barriers must exist before anything arrives on them
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+    }
     ptx::tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
 
@@ -225,32 +275,40 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         if (lane == 0) {
             uint32_t stage = 0, phase = 0, issued = 0;
             bool     ok = true;
-            for (uint32_t w = blockIdx.x; ok && w < p.num_work; w += gridDim.x) {
-                const WorkCoord c = decode_work(p, w, BN);
+            for (uint32_t w = unit; ok && w < p.num_work; w += units) {
+                const WorkCoord c  = decode_work(p, w, BN, BLOCK_M * CL);
+                const int32_t   am = static_cast<int32_t>(c.m0 + rank * BLOCK_M);
+                const int32_t   bn = static_cast<int32_t>(c.n0 + rank * BN_CTA);
                 for (uint32_t kb = c.kb0; kb < c.kb1; ++kb) {
                     ok = bounded_wait(ptx::smem_u32(&s_empty[stage]), phase ^ 1u, &s_abort,
                                       p.status, ST_PRODUCER_WAIT);
                     if (!ok) break;
-                    const uint32_t bar = ptx::smem_u32(&s_full[stage]);
-                    const uint32_t sa  = ring + stage * STAGE_BYTES;
-                    const uint32_t sb  = sa + A_TILE_BYTES;
-                    const int32_t  k0  = static_cast<int32_t>(kb * BLOCK_K);
-                    ptx::mbar_expect_tx(bar, STAGE_BYTES);
+                    const uint32_t sa = ring + stage * STAGE_BYTES;
+                    const uint32_t sb = sa + A_TILE_BYTES;
+                    const int32_t  k0 = static_cast<int32_t>(kb * BLOCK_K);
+                    uint32_t       bar = ptx::smem_u32(&s_full[stage]);
+                    if constexpr (CL == 2) {
+                        // Rank 0 owns the pair's full barrier and expects both CTAs' bytes.
+                        if (rank == 0) ptx::mbar_expect_tx(bar, 2 * STAGE_BYTES);
+                        bar = ptx::mapa_u32(bar, 0);
+                    } else {
+                        ptx::mbar_expect_tx(bar, STAGE_BYTES);
+                    }
                     if (p.a_mn_major == 0u) {
-                        ptx::tma_load_3d(sa, &tmA, bar, k0, c.m0, c.z_in);
+                        tma_load<CL>(sa, &tmA, bar, k0, am, c.z_in);
                     } else {
 #pragma unroll
                         for (int j = 0; j < BLOCK_M / 64; ++j)
-                            ptx::tma_load_3d(sa + j * (64 * BLOCK_K * 2), &tmA, bar,
-                                             c.m0 + j * 64, k0, c.z_in);
+                            tma_load<CL>(sa + j * (64 * BLOCK_K * 2), &tmA, bar, am + j * 64, k0,
+                                         c.z_in);
                     }
                     if (p.b_mn_major == 0u) {
-                        ptx::tma_load_3d(sb, &tmB, bar, k0, c.n0, c.z_in);
+                        tma_load<CL>(sb, &tmB, bar, k0, bn, c.z_in);
                     } else {
 #pragma unroll
-                        for (int j = 0; j < BN / 64; ++j)
-                            ptx::tma_load_3d(sb + j * (64 * BLOCK_K * 2), &tmB, bar,
-                                             c.n0 + j * 64, k0, c.z_in);
+                        for (int j = 0; j < BN_CTA / 64; ++j)
+                            tma_load<CL>(sb + j * (64 * BLOCK_K * 2), &tmB, bar, bn + j * 64, k0,
+                                         c.z_in);
                     }
                     ++issued;
                     if (++stage == stages) {
@@ -259,7 +317,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     }
                 }
             }
-            if (s_abort != 0u) {
+            if (s_abort != 0u && rank == 0) {
                 // Gave up somewhere: let the loads already in flight land before the CTA exits.
                 const uint32_t pending = min(issued, stages);
                 for (uint32_t i = 0; i < pending; ++i) {
@@ -280,7 +338,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        if (lane == 0 && rank == 0) {
             // K-major swizzled tiles ignore the leading offset (canonical value: 16 bytes).
             const uint32_t a_lbo   = p.a_mn_major ? 64u * BLOCK_K * 2u : 16u;
             const uint32_t b_lbo   = p.b_mn_major ? 64u * BLOCK_K * 2u : 16u;
@@ -289,12 +347,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             const uint32_t b_kstep = p.b_mn_major ? (2u * 1024u) >> 4 : (UMMA_K * 2u) >> 4;
             uint32_t       stage = 0, phase = 0, it = 0;
             bool           ok = true;
-            for (uint32_t w = blockIdx.x; ok && w < p.num_work; w += gridDim.x, ++it) {
-                const WorkCoord c      = decode_work(p, w, BN);
+            for (uint32_t w = unit; ok && w < p.num_work; w += units, ++it) {
+                const WorkCoord c      = decode_work(p, w, BN, BLOCK_M * CL);
                 const uint32_t  buf    = it & 1u;
                 const uint32_t  aphase = (it >> 1) & 1u;
-                ok = bounded_wait(ptx::smem_u32(&s_tempty[buf]), aphase ^ 1u, &s_abort, p.status,
-                                  ST_MMA_WAIT_ACC);
+                ok = bounded_wait<CL == 2>(ptx::smem_u32(&s_tempty[buf]), aphase ^ 1u, &s_abort,
+                                           p.status, ST_MMA_WAIT_ACC);
                 if (!ok) break;
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
@@ -309,20 +367,22 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     const uint64_t bd = ptx::make_smem_desc(sb, b_lbo, 1024u);
 #pragma unroll
                     for (uint32_t k = 0; k < BLOCK_K / UMMA_K; ++k) {
-                        ptx::umma_f16<1>(d_tmem, ad + k * a_kstep, bd + k * b_kstep, p.idesc,
-                                         (kb > c.kb0 || k > 0u) ? 1u : 0u);
+                        ptx::umma_f16<CL>(d_tmem, ad + k * a_kstep, bd + k * b_kstep, p.idesc,
+                                          (kb > c.kb0 || k > 0u) ? 1u : 0u);
                     }
-                    ptx::umma_commit(ptx::smem_u32(&s_empty[stage])); // slot free when MMAs retire
+                    // Slot free (in both CTAs of a pair) once these MMAs retire.
+                    umma_arrive<CL>(ptx::smem_u32(&s_empty[stage]));
                     if (++stage == stages) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
                 if (!ok) break;
-                ptx::umma_commit(ptx::smem_u32(&s_tfull[buf])); // accumulator complete
+                umma_arrive<CL>(ptx::smem_u32(&s_tfull[buf])); // accumulator complete
             }
             // All MMAs must have retired before TMEM is released and shared memory goes away.
-            ptx::umma_commit(ptx::smem_u32(&s_drain));
+            if constexpr (CL == 2) ptx::umma_commit_pair(ptx::smem_u32(&s_drain), 0x1);
+            else ptx::umma_commit(ptx::smem_u32(&s_drain));
             const uint64_t t0 = ptx::global_timer_ns();
             while (!ptx::mbar_try_wait(ptx::smem_u32(&s_drain), 0u)) {
                 if (ptx::global_timer_ns() - t0 > WAIT_LIMIT_NS) {
@@ -337,8 +397,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         const uint32_t stg  = epi + q * 2u * EPI_BUF_BYTES;
         uint32_t       it   = 0, nstore = 0;
         bool           ok   = true;
-        for (uint32_t w = blockIdx.x; ok && w < p.num_work; w += gridDim.x, ++it) {
-            const WorkCoord c      = decode_work(p, w, BN);
+        for (uint32_t w = unit; ok && w < p.num_work; w += units, ++it) {
+            const WorkCoord c      = decode_work(p, w, BN, BLOCK_M * CL);
             const uint32_t  buf    = it & 1u;
             const uint32_t  aphase = (it >> 1) & 1u;
             ok = bounded_wait(ptx::smem_u32(&s_tfull[buf]), aphase, &s_abort, p.status,
@@ -346,7 +406,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             ok = __all_sync(0xffffffffu, ok); // warp-uniform: the TMEM loads below are aligned
             if (!ok) break;
             ptx::tc_fence_after();
-            const uint32_t row0     = c.m0 + q * 32u;
+            const uint32_t row0     = c.m0 + rank * BLOCK_M + q * 32u;
             const bool     row_live = row0 < p.M;
 #pragma unroll 1
             for (int ch = 0; ch < NCHUNK; ++ch) {
@@ -367,10 +427,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     }
                 }
                 if (ch == NCHUNK - 1) {
-                    // Accumulator fully read: hand it back to the MMA issuer.
+                    // Accumulator fully read: hand it back to the MMA issuer (rank 0).
                     ptx::tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&s_tempty[buf]));
+                    if (lane == 0) {
+                        if constexpr (CL == 2) ptx::mbar_arrive_cluster(ptx::smem_u32(&s_tempty[buf]), 0);
+                        else ptx::mbar_arrive(ptx::smem_u32(&s_tempty[buf]));
+                    }
                 }
                 const uint32_t col0 = c.n0 + ch * CH;
                 if (row_live && col0 < p.N) {
@@ -400,10 +463,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     // ---------------------------------------------------------------------- tail
     ptx::tc_fence_before();
     __syncthreads();
+    if constexpr (CL == 2) { // neither CTA may leave while its peer can still touch it
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+    }
     if (warp == 1) {
         ptx::tc_fence_after();
         __syncwarp();
-        ptx::tmem_dealloc<1>(tmem_base, TMEM_COLS);
+        ptx::tmem_dealloc<CL>(tmem_base, TMEM_COLS);
     }
 }
 

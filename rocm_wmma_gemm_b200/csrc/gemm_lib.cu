@@ -13,6 +13,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <limits>
 #include <mutex>
@@ -150,6 +151,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 struct DeviceCtx {
     bool          ready    = false;
     int           sm_count = 0;
+    int           pair_units[2] = {0, 0}; // co-resident CTA pairs for tile_n 128 / 256 (0 = not asked yet)
     unsigned int* d_status = nullptr;
     // host-buffer path
     cudaStream_t h_stream = nullptr;
@@ -162,12 +164,25 @@ static DeviceCtx     g_ctx[k_max_devices];
 static std::mutex    g_mutex;
 static EncodeTiledFn g_encode = nullptr;
 
-template <int BN, int OUT>
+template <int BN, int OUT, int CL>
+static cudaError_t set_smem_attr_one()
+{
+    cudaError_t e = cudaFuncSetAttribute(gemm_umma_kernel<BN, OUT, CL>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)gemm_smem_bytes(BN, CL, max_stages(BN, CL)));
+    if (e == cudaSuccess && CL == 2)
+        e = cudaFuncSetAttribute(gemm_umma_kernel<BN, OUT, CL>,
+                                 cudaFuncAttributeNonPortableClusterSizeAllowed, 0);
+    return e;
+}
+
+template <int BN, int CL>
 static cudaError_t set_smem_attr()
 {
-    return cudaFuncSetAttribute(gemm_umma_kernel<BN, OUT>,
-                                cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                (int)gemm_smem_bytes(BN, BN == 256 ? 4 : (BN == 128 ? 6 : 8)));
+    cudaError_t e = set_smem_attr_one<BN, OUT_F32, CL>();
+    if (e == cudaSuccess) e = set_smem_attr_one<BN, OUT_F16, CL>();
+    if (e == cudaSuccess) e = set_smem_attr_one<BN, OUT_BF16, CL>();
+    return e;
 }
 
 static int get_ctx(DeviceCtx** out)
@@ -198,15 +213,11 @@ static int get_ctx(DeviceCtx** out)
         }
         CUDA_TRY(cudaMalloc(&c.d_status, sizeof(unsigned int)));
         CUDA_TRY(cudaMemset(c.d_status, 0, sizeof(unsigned int)));
-        CUDA_TRY((set_smem_attr<64, OUT_F32>()));
-        CUDA_TRY((set_smem_attr<64, OUT_F16>()));
-        CUDA_TRY((set_smem_attr<64, OUT_BF16>()));
-        CUDA_TRY((set_smem_attr<128, OUT_F32>()));
-        CUDA_TRY((set_smem_attr<128, OUT_F16>()));
-        CUDA_TRY((set_smem_attr<128, OUT_BF16>()));
-        CUDA_TRY((set_smem_attr<256, OUT_F32>()));
-        CUDA_TRY((set_smem_attr<256, OUT_F16>()));
-        CUDA_TRY((set_smem_attr<256, OUT_BF16>()));
+        CUDA_TRY((set_smem_attr<64, 1>()));
+        CUDA_TRY((set_smem_attr<128, 1>()));
+        CUDA_TRY((set_smem_attr<256, 1>()));
+        CUDA_TRY((set_smem_attr<128, 2>()));
+        CUDA_TRY((set_smem_attr<256, 2>()));
         c.ready = true;
     }
     *out = &c;
@@ -304,14 +315,14 @@ static bool tma_ok(const Problem& p, const View& v)
 // ------------------------------------------------------------------------------------------
 // Configuration handling
 // ------------------------------------------------------------------------------------------
-static int max_stages_for(int tile_n) { return tile_n == 256 ? 4 : (tile_n == 128 ? 6 : 8); }
-
 static int check_config(const b200_gemm_config& c)
 {
-    if (c.tile_m != 128) return fail(B200_GEMM_ERR_BAD_CONFIG, "tile_m %d not compiled (128 only)", c.tile_m);
+    if (c.cluster != 1 && c.cluster != 2) return fail(B200_GEMM_ERR_BAD_CONFIG, "cluster %d not compiled (1 or 2)", c.cluster);
+    if (c.tile_m != 128 * c.cluster)
+        return fail(B200_GEMM_ERR_BAD_CONFIG, "tile_m %d does not match cluster %d (tile_m = 128 * cluster)", c.tile_m, c.cluster);
     if (c.tile_n != 64 && c.tile_n != 128 && c.tile_n != 256)
         return fail(B200_GEMM_ERR_BAD_CONFIG, "tile_n %d not compiled (64, 128, 256)", c.tile_n);
-    if (c.cluster != 1) return fail(B200_GEMM_ERR_BAD_CONFIG, "cluster %d not compiled (1 only)", c.cluster);
+    if (c.cluster == 2 && c.tile_n == 64) return fail(B200_GEMM_ERR_BAD_CONFIG, "tile_n 64 needs cluster 1");
     if (c.stages < 2 || c.stages > MAX_STAGES) return fail(B200_GEMM_ERR_BAD_CONFIG, "stages %d outside 2..%d", c.stages, MAX_STAGES);
     if (c.split_k < 1 || c.split_k > 64) return fail(B200_GEMM_ERR_BAD_CONFIG, "split_k %d outside 1..64", c.split_k);
     if (c.raster < 0 || c.raster > 64) return fail(B200_GEMM_ERR_BAD_CONFIG, "raster %d outside 0..64", c.raster);
@@ -322,7 +333,7 @@ static int check_config(const b200_gemm_config& c)
 // holds and give every K partition at least one k-block.
 static void legalize(b200_gemm_config& c, const View& v, uint32_t* kb_per_split)
 {
-    const int ms = max_stages_for(c.tile_n);
+    const int ms = max_stages(c.tile_n, c.cluster);
     if (c.stages > ms) c.stages = ms;
     const uint32_t k_blocks = (v.K + BLOCK_K - 1) / BLOCK_K;
     uint32_t       split    = (uint32_t)c.split_k;
@@ -334,11 +345,29 @@ static void legalize(b200_gemm_config& c, const View& v, uint32_t* kb_per_split)
     *kb_per_split      = per;
 }
 
+// Debugging / profiling override: B200_GEMM_CONFIG="tile_m,tile_n,stages,cluster,split_k,raster"
+// replaces the table's choice for every call that does not pass an explicit config.
+static bool env_config(b200_gemm_config* out)
+{
+    const char* e = getenv("B200_GEMM_CONFIG");
+    if (!e || !*e) return false;
+    b200_gemm_config c;
+    if (sscanf(e, "%d,%d,%d,%d,%d,%d", &c.tile_m, &c.tile_n, &c.stages, &c.cluster, &c.split_k, &c.raster) != 6)
+        return false;
+    *out = c;
+    return true;
+}
+
 static b200_gemm_config resolve_config(const Problem& p, const b200_gemm_config* user, int* idx)
 {
     if (user) {
         if (idx) *idx = -1;
         return *user;
+    }
+    b200_gemm_config forced;
+    if (env_config(&forced)) {
+        if (idx) *idx = -1;
+        return forced;
     }
     const int i = find_best_config(p.M, p.N, p.K, out_is_f32(p.types) ? 1 : 0, p.la, p.lb, p.lc);
     if (idx) *idx = i;
@@ -377,16 +406,53 @@ static int encode_operand(CUtensorMap* tm, bool bf16, const void* base, uint32_t
 // ------------------------------------------------------------------------------------------
 // Launch
 // ------------------------------------------------------------------------------------------
-template <int BN>
-static cudaError_t launch_bn(int out, dim3 grid, uint32_t smem, cudaStream_t s, const CUtensorMap& a,
-                             const CUtensorMap& b, const CUtensorMap& d, const GemmParams& gp)
+template <int BN, int CL>
+static cudaError_t launch_bn(int out, uint32_t units_wanted, int* pair_units, uint32_t smem, cudaStream_t s,
+                             const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& d,
+                             const GemmParams& gp)
 {
-    switch (out) {
-        case OUT_F32: gemm_umma_kernel<BN, OUT_F32><<<grid, GEMM_THREADS, smem, s>>>(a, b, d, gp); break;
-        case OUT_F16: gemm_umma_kernel<BN, OUT_F16><<<grid, GEMM_THREADS, smem, s>>>(a, b, d, gp); break;
-        default: gemm_umma_kernel<BN, OUT_BF16><<<grid, GEMM_THREADS, smem, s>>>(a, b, d, gp); break;
+    cudaLaunchConfig_t lc = {};
+    dim3               grid(CL * units_wanted);
+    if (CL == 2) {
+        // A persistent pair kernel wants exactly as many clusters as can be resident at once.
+        if (*pair_units == 0) {
+            cudaLaunchConfig_t q = {};
+            q.gridDim            = dim3(2 * 148);
+            q.blockDim           = dim3(GEMM_THREADS);
+            q.dynamicSmemBytes   = smem;
+            cudaLaunchAttribute qa[1];
+            qa[0].id               = cudaLaunchAttributeClusterDimension;
+            qa[0].val.clusterDim.x = 2;
+            qa[0].val.clusterDim.y = 1;
+            qa[0].val.clusterDim.z = 1;
+            q.attrs                = qa;
+            q.numAttrs             = 1;
+            int         n  = 0;
+            cudaError_t qe = cudaOccupancyMaxActiveClusters(&n, gemm_umma_kernel<BN, OUT_F32, CL>, &q);
+            if (qe != cudaSuccess || n < 1) {
+                (void)cudaGetLastError();
+                n = 64;
+            }
+            *pair_units = n;
+        }
+        grid = dim3(2 * std::min<uint32_t>(units_wanted, (uint32_t)*pair_units));
     }
-    return cudaGetLastError();
+    lc.gridDim            = grid;
+    lc.blockDim           = dim3(GEMM_THREADS);
+    lc.dynamicSmemBytes   = smem;
+    lc.stream             = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id               = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CL;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    lc.attrs                 = attr;
+    lc.numAttrs              = 1;
+    switch (out) {
+        case OUT_F32: return cudaLaunchKernelEx(&lc, gemm_umma_kernel<BN, OUT_F32, CL>, a, b, d, gp);
+        case OUT_F16: return cudaLaunchKernelEx(&lc, gemm_umma_kernel<BN, OUT_F16, CL>, a, b, d, gp);
+        default: return cudaLaunchKernelEx(&lc, gemm_umma_kernel<BN, OUT_BF16, CL>, a, b, d, gp);
+    }
 }
 
 template <class TIn, class TOut>
@@ -454,7 +520,8 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     gp.N            = v.N;
     gp.K            = v.K;
     gp.batch        = (uint32_t)p.batch;
-    gp.m_tiles      = (v.M + BLOCK_M - 1) / BLOCK_M;
+    const uint32_t cl   = (uint32_t)cfg.cluster;
+    gp.m_tiles      = (v.M + BLOCK_M * cl - 1) / (BLOCK_M * cl);
     gp.n_tiles      = (v.N + bn - 1) / bn;
     gp.k_blocks     = (v.K + BLOCK_K - 1) / BLOCK_K;
     gp.split_k      = split;
@@ -467,9 +534,9 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     gp.b_mn_major = v.b_mn ? 1u : 0u;
     // tcgen05 instruction descriptor, kind::f16: [4,6) D format (1 = f32); [7,10) A format and
     // [10,13) B format (0 = f16, 1 = bf16); bit 15 / 16: A / B is MN-major; [17,23) N >> 3;
-    // [24,29) M >> 4.
+    // [24,29) M >> 4 (M = 256 for a CTA pair).
     gp.idesc = (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | (gp.a_mn_major << 15) |
-               (gp.b_mn_major << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BLOCK_M >> 4) << 24);
+               (gp.b_mn_major << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)((BLOCK_M * cl) >> 4) << 24);
     gp.stages = (uint32_t)cfg.stages;
     gp.status = ctx->d_status;
 
@@ -483,7 +550,7 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
 
     CUtensorMap tmA, tmB, tmD;
     st = encode_operand(&tmA, bf16, v.a, v.M, v.K, p.batch, v.a_mn, BLOCK_M);
-    if (st == B200_GEMM_OK) st = encode_operand(&tmB, bf16, v.b, v.N, v.K, p.batch, v.b_mn, (uint32_t)bn);
+    if (st == B200_GEMM_OK) st = encode_operand(&tmB, bf16, v.b, v.N, v.K, p.batch, v.b_mn, (uint32_t)bn / cl);
     if (st == B200_GEMM_OK) {
         if (split > 1)
             st = encode_map(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ws, v.N, v.M, (uint64_t)p.batch * split, 32, 32);
@@ -498,14 +565,19 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
         return st;
     }
 
-    const uint32_t smem     = gemm_smem_bytes(bn, cfg.stages);
-    const dim3     grid(std::min<uint32_t>(gp.num_work, (uint32_t)ctx->sm_count));
+    const uint32_t smem     = gemm_smem_bytes(bn, (int)cl, cfg.stages);
+    const uint32_t units    = std::min<uint32_t>(gp.num_work, (uint32_t)ctx->sm_count / cl);
     const int      kern_out = split > 1 ? OUT_F32 : out;
     cudaError_t    e;
-    switch (bn) {
-        case 64: e = launch_bn<64>(kern_out, grid, smem, stream, tmA, tmB, tmD, gp); break;
-        case 128: e = launch_bn<128>(kern_out, grid, smem, stream, tmA, tmB, tmD, gp); break;
-        default: e = launch_bn<256>(kern_out, grid, smem, stream, tmA, tmB, tmD, gp); break;
+    if (cl == 2) {
+        if (bn == 128) e = launch_bn<128, 2>(kern_out, units, &ctx->pair_units[0], smem, stream, tmA, tmB, tmD, gp);
+        else e = launch_bn<256, 2>(kern_out, units, &ctx->pair_units[1], smem, stream, tmA, tmB, tmD, gp);
+    } else {
+        switch (bn) {
+            case 64: e = launch_bn<64, 1>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
+            case 128: e = launch_bn<128, 1>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
+            default: e = launch_bn<256, 1>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
+        }
     }
     g_launches.fetch_add(1, std::memory_order_relaxed);
     if (e != cudaSuccess) {

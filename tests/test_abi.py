@@ -1,0 +1,123 @@
+"""CPU tests of the C-ABI boundary: the library loads without a GPU, exports every symbol
+include/b200_gemm.h declares, validates arguments like the header says, and never computes
+on the CPU."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "b200_gemm.h")
+
+
+def declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = re.findall(r"\b([a-z][a-z0-9_]*)\s*\(", text)
+    return sorted({n for n in names if n.startswith(("b200_gemm_", "rocm_wmma_gemm_"))})
+
+
+def test_header_declares_the_reference_symbols():
+    names = declared_functions()
+    for suffix in ("f16_f16", "f32_f16", "bf16_bf16", "f32_bf16"):
+        assert f"rocm_wmma_gemm_{suffix}" in names
+        assert f"b200_gemm_{suffix}" in names
+
+
+def test_library_exports_every_declared_symbol(gemm_lib):
+    lib = gemm_lib.lib()
+    names = declared_functions()
+    assert len(names) >= 18
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in b200_gemm.h but not exported"
+        assert n in gemm_lib.ABI_SYMBOLS, f"{n} has no ctypes signature"
+    assert set(gemm_lib.ABI_SYMBOLS) == set(names)
+
+
+def test_no_oracle_or_cpu_path_in_the_product():
+    """The product sources never reference the oracle."""
+    pkg = os.path.join(ROOT, "rocm_wmma_gemm_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".cpp", ".hpp", ".h", ".inc")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.lower(), os.path.join(dirpath, f)
+
+
+def _call(g, name, *args):
+    return getattr(g.lib(), name)(*args)
+
+
+def test_argument_validation_needs_no_device(gemm_lib):
+    g = gemm_lib
+    lib = g.lib()
+    p = 0x1000  # never dereferenced: validation fails first
+    assert lib.b200_gemm_f32_f16(p, p, p, 128, 128, 128, 1, 2, 0, 0, None) == 1  # bad layout
+    assert b"layout" in lib.b200_gemm_last_error()
+    assert lib.b200_gemm_f32_f16(p, p, p, 128, 128, 128, 1, 0, -1, 0, None) == 1
+    assert lib.b200_gemm_f32_f16(None, p, p, 128, 128, 128, 1, 0, 0, 0, None) == 2  # NULL C
+    assert lib.b200_gemm_f16_f16(p, None, p, 128, 128, 128, 1, 0, 0, 0, None) == 2
+    assert lib.b200_gemm_f32_f16(p, p, p, 128, 128, 128, 0, 0, 0, 0, None) == 3  # batch 0
+    assert lib.b200_gemm_f32_f16(p, p, p, 2 ** 31, 128, 128, 1, 0, 0, 0, None) == 3
+    assert lib.b200_gemm_f32_f16(p + 2, p, p, 128, 128, 128, 1, 0, 0, 0, None) == 4  # f32 C at 2 mod 4
+    assert lib.b200_gemm_bf16_bf16(p, p + 1, p, 128, 128, 128, 1, 0, 0, 0, None) == 4
+    # Empty C: nothing to do, succeeds anywhere.
+    assert lib.b200_gemm_f32_f16(None, None, None, 0, 128, 128, 1, 0, 0, 0, None) == 0
+    assert lib.b200_gemm_f32_f16(None, None, None, 128, 0, 128, 1, 1, 1, 1, None) == 0
+    # The void reference symbols record instead of returning.
+    lib.rocm_wmma_gemm_f32_bf16(p, p, p, 128, 128, 128, 1, 7, 0, 0, None)
+    assert lib.b200_gemm_last_status() == 1
+    lib.rocm_wmma_gemm_f32_bf16(None, None, None, 0, 0, 0, 1, 0, 0, 0, None)
+    assert lib.b200_gemm_last_status() == 0
+    assert lib.b200_gemm_ex(9, p, p, p, 8, 8, 8, 1, 0, 0, 0, None, None) == 7  # unknown type pair
+
+
+def test_no_cpu_fallback(gemm_lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present; this checks the GPU-less behaviour")
+    lib = gemm_lib.lib()
+    buf = (ctypes.c_float * (128 * 128))()
+    p = ctypes.addressof(buf)
+    assert lib.b200_gemm_f32_f16(p, p, p, 128, 128, 128, 1, 0, 0, 0, None) == 5  # B200_GEMM_ERR_NO_DEVICE
+    assert lib.b200_gemm_host(1, p, p, p, 128, 128, 128, 1, 0, 0, 0) == 5
+    with pytest.raises(gemm_lib.GemmError):
+        gemm_lib.loader().gemm(p, p, p, 128, 128, 128, types=("f32", "f16"))
+
+
+def test_slab_partition(gemm_lib):
+    g = gemm_lib
+    for n in (16384, 32768, 8192, 1000, 255, 1):
+        for world in (1, 2, 3, 4, 8):
+            for align in (1, 64, 256):
+                covered = 0
+                for r in range(world):
+                    b, c = g.slab(n, world, r, align)
+                    assert b == covered or c == 0
+                    if r < world - 1 and b + c < n:
+                        assert c % align == 0
+                    covered = b + c if c else covered
+                assert covered == n
+    assert g.slab(16384, 8, 3, 256) == (6144, 2048)
+    with pytest.raises(g.GemmError):
+        g.slab(100, 4, 4)
+
+
+def test_explicit_config_is_validated(gemm_lib):
+    g = gemm_lib
+    lib = g.lib()
+    p = 0x1000
+    bad = [g.GemmConfig(128, 96, 4, 1, 1, 8), g.GemmConfig(256, 256, 4, 1, 1, 8), g.GemmConfig(128, 256, 4, 2, 1, 8),
+           g.GemmConfig(256, 64, 4, 2, 1, 8), g.GemmConfig(128, 128, 1, 1, 1, 8), g.GemmConfig(128, 128, 4, 1, 0, 8),
+           g.GemmConfig(128, 128, 4, 3, 1, 8)]
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("explicit-config validation on a GPU is covered by the parity tests")
+    for cfg in bad:  # without a device the call stops at NO_DEVICE before config checks
+        assert lib.b200_gemm_ex(1, p, p, p, 128, 128, 128, 1, 0, 0, 0, None, ctypes.byref(cfg)) in (5, 7)
+
+
+def test_version_and_counters(gemm_lib):
+    assert b"sm_100a" in gemm_lib.lib().b200_gemm_version()
+    assert gemm_lib.launch_count() >= 0

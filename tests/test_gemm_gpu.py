@@ -1,0 +1,261 @@
+"""GPU parity tests: the sm_100a kernels, called through the C ABI, against the CPU oracle on
+the same seeded inputs.  Shapes, layouts and tolerances follow the reference's own tests
+(test/gemm/test_float_accum.cpp:149-224, test/gemm/test_same_prec.cpp:138-213)."""
+import itertools
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import rocm_wmma_gemm_b200 as g
+from gpu_util import NAMES, as_f32, check_parity, f32_sum_tolerance, gpu_gemm, loader, to_device
+
+pytestmark = pytest.mark.gpu
+
+# The 13 shapes of the reference's typed tests.
+REF_SHAPES = [(128, 128, 128), (128, 256, 128), (128, 128, 256), (256, 128, 128), (256, 256, 256),
+              (320, 320, 320), (320, 512, 512), (512, 320, 320), (512, 512, 320), (512, 320, 512),
+              (512, 512, 512), (1024, 256, 256), (256, 1024, 256)]
+LAYOUTS = list(itertools.product((0, 1), repeat=3))  # (layout_a, layout_b, layout_c)
+SIGMA_UNIFORM = 1.0 / 3.0  # std of the product of two uniform[-1,1] values
+
+
+def seeded(M, N, K, la, lb, bf16):
+    return oracle.init_matrix(M, K, la, bf16), oracle.init_matrix(K, N, lb, bf16)
+
+
+@pytest.mark.parametrize("types", range(4), ids=NAMES)
+@pytest.mark.parametrize("la,lb,lc", LAYOUTS, ids=["".join("rc"[x] for x in l) for l in LAYOUTS])
+def test_reference_shapes(types, la, lb, lc):
+    bf16 = types >= 2
+    for (M, N, K) in REF_SHAPES:
+        A, B = seeded(M, N, K, la, lb, bf16)
+        ref = oracle.hgemm(types, A, B, M, N, K, lc, la, lb)
+        got = gpu_gemm(types, A, B, M, N, K, lc, la, lb)
+        check_parity(types, got, ref, K, SIGMA_UNIFORM, M, N, lc)
+
+
+def test_config1_known_answer():
+    """BASELINE config 1: fp16 -> f32, 256^3, A row / B col / C row, through the void
+    reference symbol `rocm_wmma_gemm_f32_f16`."""
+    A, B = seeded(256, 256, 256, 0, 1, False)
+    got = gpu_gemm(1, A, B, 256, 256, 256, 0, 0, 1, checked=False)
+    assert g.lib().b200_gemm_last_status() == 0
+    ref = oracle.hgemm(1, A, B, 256, 256, 256, 0, 0, 1)
+    rel, mx = check_parity(1, got, ref, 256, SIGMA_UNIFORM, 256, 256, 0)
+    assert abs(got[0] - (-4.48529482)) < 1e-4 and abs(got[-1] - (-0.209937096)) < 1e-4
+    assert abs(np.sqrt((got.astype(np.float64) ** 2).sum()) - 1361.53624) < 1e-2
+
+
+CONFIGS = [g.GemmConfig(128, 64, 8, 1, 1, 8), g.GemmConfig(128, 128, 6, 1, 1, 4), g.GemmConfig(128, 256, 4, 1, 1, 0),
+           g.GemmConfig(256, 128, 8, 2, 1, 2), g.GemmConfig(256, 256, 6, 2, 1, 16), g.GemmConfig(128, 128, 2, 1, 1, 1),
+           g.GemmConfig(256, 256, 3, 2, 1, 1)]
+
+
+@pytest.mark.parametrize("cfg", CONFIGS, ids=[f"m{c.tile_m}n{c.tile_n}s{c.stages}c{c.cluster}r{c.raster}" for c in CONFIGS])
+def test_every_compiled_variant_every_layout(cfg):
+    """Each tile variant, for all 8 layouts and 4 type pairs, on an aligned and a ragged shape."""
+    for types in range(4):
+        bf16 = types >= 2
+        for (la, lb, lc) in LAYOUTS:
+            for (M, N, K) in [(384, 640, 192), (264, 136, 200)]:
+                A, B = seeded(M, N, K, la, lb, bf16)
+                ref = oracle.hgemm(types, A, B, M, N, K, lc, la, lb)
+                got = gpu_gemm(types, A, B, M, N, K, lc, la, lb, config=cfg)
+                check_parity(types, got, ref, K, SIGMA_UNIFORM, M, N, lc)
+
+
+RAGGED = [(8, 8, 8), (16, 8, 24), (1, 1, 1), (3, 5, 7), (127, 129, 65), (1000, 1000, 1000), (129, 8, 4096),
+          (8, 1032, 72), (250, 250, 16), (17, 33, 9)]
+
+
+@pytest.mark.parametrize("M,N,K", RAGGED)
+def test_ragged_and_tiny_shapes(M, N, K):
+    """Edge tiles, K tails and sizes whose rows TMA cannot address (odd leading dimensions go
+    through the CUDA-core kernel).  The reference's kernel has no K tail and no load bounds
+    checks; this library accepts any size."""
+    for types in (1, 2):
+        bf16 = types >= 2
+        for (la, lb, lc) in [(0, 1, 0), (1, 0, 1), (0, 0, 0), (1, 1, 1)]:
+            A, B = seeded(M, N, K, la, lb, bf16)
+            ref = oracle.hgemm(types, A, B, M, N, K, lc, la, lb)
+            got = gpu_gemm(types, A, B, M, N, K, lc, la, lb)
+            check_parity(types, got, ref, K, SIGMA_UNIFORM, M, N, lc)
+
+
+def test_empty_inputs():
+    l = loader()
+    c = torch.full((64,), 7.0, device="cuda")
+    a = torch.zeros(64, dtype=torch.float16, device="cuda")
+    l.gemm(c, a, a, 0, 8, 8)       # M == 0: no-op
+    l.gemm(c, a, a, 8, 0, 8)       # N == 0: no-op
+    torch.cuda.synchronize()
+    assert (c == 7.0).all()
+    l.gemm(c, a, a, 8, 8, 0)       # K == 0: the empty sum, C = 0
+    torch.cuda.synchronize()
+    assert (c == 0.0).all()
+
+
+@pytest.mark.parametrize("types", range(4), ids=NAMES)
+def test_strided_batched(types):
+    """batch_count > 1 with the reference's strides M*K, K*N, M*N (kernel/kernel.hpp:165-167);
+    the reference ships no batched test."""
+    bf16 = types >= 2
+    M, N, K, batch = 192, 320, 256, 5
+    for (la, lb, lc) in [(0, 1, 0), (1, 0, 0), (0, 0, 1), (1, 1, 1)]:
+        # distinct values per batch: rotate the seeded stream
+        A = np.concatenate([oracle.init_matrix(M, K, la, bf16)[(np.arange(M * K) + 97 * b) % (M * K)] for b in range(batch)])
+        B = np.concatenate([oracle.init_matrix(K, N, lb, bf16)[(np.arange(K * N) + 31 * b) % (K * N)] for b in range(batch)])
+        got = gpu_gemm(types, A, B, M, N, K, lc, la, lb, batch=batch)
+        for b in range(batch):
+            ref = oracle.hgemm(types, A[b * M * K:(b + 1) * M * K], B[b * K * N:(b + 1) * K * N], M, N, K, lc, la, lb)
+            check_parity(types, got[b * M * N:(b + 1) * M * N], ref, K, SIGMA_UNIFORM, M, N, lc)
+        # an unaligned batched case goes through the CUDA-core kernel
+    A = np.concatenate([oracle.init_matrix(9, 7, 0, bf16)] * 3)
+    B = np.concatenate([oracle.init_matrix(7, 5, 1, bf16)] * 3)
+    got = gpu_gemm(types, A, B, 9, 5, 7, 0, 0, 1, batch=3)
+    ref = oracle.hgemm(types, A[:63], B[:35], 9, 5, 7, 0, 0, 1)
+    for b in range(3):
+        check_parity(types, got[b * 45:(b + 1) * 45], ref, 7, SIGMA_UNIFORM, 9, 5, 0)
+
+
+@pytest.mark.parametrize("split_k", [2, 3, 8, 64])
+def test_split_k(split_k):
+    """K partitions through the f32 workspace + deterministic reduction."""
+    M, N, K = 128, 384, 2048 + 64
+    for types in range(4):
+        bf16 = types >= 2
+        for (la, lb, lc), cl in [((0, 1, 0), 1), ((1, 0, 1), 1), ((0, 0, 0), 2)]:
+            A, B = seeded(M, N, K, la, lb, bf16)
+            ref = oracle.hgemm(types, A, B, M, N, K, lc, la, lb)
+            cfg = g.GemmConfig(128 * cl, 128, 4, cl, split_k, 8)
+            got = gpu_gemm(types, A, B, M, N, K, lc, la, lb, config=cfg)
+            check_parity(types, got, ref, K, SIGMA_UNIFORM, M, N, lc)
+            again = gpu_gemm(types, A, B, M, N, K, lc, la, lb, config=cfg)
+            assert np.array_equal(got.view(np.uint8), again.view(np.uint8)), "split-K must be deterministic"
+
+
+def test_all_layouts_agree():
+    """The same logical product through all 8 layouts gives the same C (tight tolerance: the
+    products are identical, only tile shapes and operand roles differ)."""
+    M, N, K = 512, 384, 640
+    rng = np.random.default_rng(7)
+    A = torch.from_numpy(rng.uniform(-1, 1, (M, K)).astype(np.float32)).to(torch.bfloat16)
+    B = torch.from_numpy(rng.uniform(-1, 1, (K, N)).astype(np.float32)).to(torch.bfloat16)
+    results = []
+    for (la, lb, lc) in LAYOUTS:
+        Am = (A if la == 0 else A.t()).contiguous().view(torch.int16).numpy().view(np.uint16).ravel()
+        Bm = (B if lb == 0 else B.t()).contiguous().view(torch.int16).numpy().view(np.uint16).ravel()
+        C = gpu_gemm(3, Am, Bm, M, N, K, lc, la, lb)
+        results.append(C.reshape(M, N) if lc == 0 else C.reshape(N, M).T)
+    for r in results[1:]:
+        assert np.abs(r - results[0]).max() <= 2e-5
+
+
+def test_host_buffer_entry_point():
+    """b200_gemm_host: host pointers in, host pointers out, copies inside the call."""
+    M, N, K = 320, 512, 448
+    for types in range(4):
+        bf16 = types >= 2
+        A, B = seeded(M, N, K, 0, 1, bf16)
+        ta, tb = torch.from_numpy(A.view(np.int16)).pin_memory(), torch.from_numpy(B.view(np.int16))
+        tc = torch.empty(M * N, dtype=torch.float32 if types in (1, 3) else torch.int16)
+        loader().gemm_host(tc, ta, tb, M, N, K, 0, 0, 1, types=types)
+        got = tc.numpy() if types in (1, 3) else tc.numpy().view(np.uint16)
+        ref = oracle.hgemm(types, A, B, M, N, K, 0, 0, 1)
+        check_parity(types, got, ref, K, SIGMA_UNIFORM, M, N, 0)
+
+
+def test_linearity():
+    """(A1 + A2) * B == A1*B + A2*B within f32 rounding when the sums are exact in f16
+    (small integers), at a size the CPU reference cannot cover quickly."""
+    M = N = K = 2048
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    A1 = torch.randint(-4, 5, (M, K), device="cuda", generator=gen).to(torch.float16)
+    A2 = torch.randint(-4, 5, (M, K), device="cuda", generator=gen).to(torch.float16)
+    B = torch.randint(-4, 5, (K, N), device="cuda", generator=gen).to(torch.float16)
+    l = loader()
+    outs = []
+    for A in (A1, A2, A1 + A2):
+        C = torch.empty(M, N, device="cuda", dtype=torch.float32)
+        l.gemm(C, A.contiguous(), B.contiguous(), M, N, K, 0, 0, 0)
+        outs.append(C)
+    g.device_status()
+    # integer-valued products and sums below 2^24 are exact in f32: equality is bit-exact
+    assert torch.equal(outs[0] + outs[1], outs[2])
+
+
+BIG = [
+    # (types, M, N, K, la, lb, lc, distribution, sigma)
+    (3, 8192, 8192, 8192, 0, 1, 0, ("normal", 0.02), 4e-4),       # headline shape, bf16 -> f32
+    (3, 4096, 5120, 5120, 0, 1, 0, ("normal", 0.02), 4e-4),       # projection shape
+    (0, 4096, 4096, 4096, 1, 0, 1, ("uniform", 1.0), 1.0 / 3.0),  # fp16 -> fp16 square, A col / B row / C col
+    (1, 16, 8192, 8192, 0, 0, 0, ("uniform", 1.0), 1.0 / 3.0),    # skinny, B row-major
+    (1, 128, 28672, 8192, 0, 1, 0, ("uniform", 1.0), 1.0 / 3.0),  # skinny, B col-major
+    (2, 8192, 4096, 16384, 0, 1, 0, ("normal", 1.0), 1.0),        # slab of the 16384^3 bf16 -> bf16 problem
+]
+
+
+@pytest.mark.parametrize("types,M,N,K,la,lb,lc,dist,sigma", BIG,
+                         ids=[f"{NAMES[b[0]]}-{b[1]}x{b[2]}x{b[3]}" for b in BIG])
+def test_full_size_sampled_rows_and_columns(types, M, N, K, la, lb, lc, dist, sigma):
+    """Full-size shapes: whole rows and whole columns of C (first/last, tile boundaries, random)
+    against the CPU oracle, which computes only the sampled elements."""
+    bf16 = types >= 2
+    dt = torch.bfloat16 if bf16 else torch.float16
+    gen = torch.Generator(device="cuda").manual_seed(M + 3 * N + 7 * K)
+
+    def make(rows, cols):
+        if dist[0] == "normal":
+            x = torch.randn(rows, cols, device="cuda", generator=gen) * dist[1]
+        else:
+            x = torch.rand(rows, cols, device="cuda", generator=gen) * 2 - 1
+        return x.to(dt)
+
+    A, B = make(M, K), make(K, N)
+    Am = (A if la == 0 else A.t()).contiguous()
+    Bm = (B if lb == 0 else B.t()).contiguous()
+    C = torch.full((M * N,), float("nan"), device="cuda").to(torch.float32 if types in (1, 3) else dt)
+    loader().gemm(C, Am, Bm, M, N, K, lc, la, lb)
+    g.device_status()
+    Cl = (C.view(M, N) if lc == 0 else C.view(N, M).t())
+    assert not torch.isnan(Cl.float()).any()
+
+    rng = np.random.default_rng(5)
+    rows = sorted(set([0, M - 1] + [r for r in (127, 128, 255, 256) if r < M] + list(rng.integers(0, M, 3))))
+    cols = sorted(set([0, N - 1] + [c for c in (255, 256, 511, 512) if c < N] + list(rng.integers(0, N, 3))))
+    A_bits = Am.view(torch.int16).cpu().numpy().view(np.uint16).ravel()
+    B_bits = Bm.view(torch.int16).cpu().numpy().view(np.uint16).ravel()
+    eps = 0.0 if types in (1, 3) else (2.0 ** -8 if bf16 else 2.0 ** -11)
+
+    def compare(got, want):
+        got, want = got.astype(np.float64), want.astype(np.float64)
+        diff = np.abs(got - want)
+        rel_fro = np.sqrt((diff ** 2).sum()) / np.sqrt((want ** 2).sum())
+        assert rel_fro <= 1e-3, rel_fro
+        # 16-bit outputs: output rounding (2 eps |ref| + eps sigma sqrt(K)); all outputs: the
+        # order-of-summation noise of an f32 sum of K products.
+        bound = 2 * eps * np.abs(want) + eps * sigma * np.sqrt(K) + f32_sum_tolerance(K, sigma)
+        assert (diff <= bound).all(), (diff - bound).max()
+
+    ref_rows = oracle.hgemm_select(types, A_bits, B_bits, M, N, K, 0, la, lb, rows=rows, cols=None)
+    ref_rows = as_f32(types, ref_rows).reshape(M, N)[rows]
+    compare(Cl[rows].float().cpu().numpy(), ref_rows)
+    ref_cols = oracle.hgemm_select(types, A_bits, B_bits, M, N, K, 0, la, lb, rows=None, cols=cols)
+    ref_cols = as_f32(types, ref_cols).reshape(M, N)[:, cols]
+    compare(Cl[:, cols].float().cpu().numpy(), ref_cols)
+
+
+def test_tuned_table_configs_run():
+    """Whatever config the table selects for the benchmark shapes is a compiled variant."""
+    for (M, N, K) in [(1024,) * 3, (2048,) * 3, (4096, 4096, 2048), (64, 8192, 8192)]:
+        for (la, lb, lc) in LAYOUTS:
+            for tg in (0, 1):
+                cfg, idx = g.get_gemm_params(M, N, K, lc, la, lb, tg)
+                assert idx >= 0 and cfg.tile_m == 128 * cfg.cluster
+
+
+def test_device_status_is_clean():
+    assert g.device_status() == 0
+    assert g.launch_count() > 0

@@ -91,7 +91,7 @@ enum b200_gemm_types {
  * (rocm_wmma_gemm/config/gemm_config_gfx1100_f16.json:1-22; struct gemm_params generated by
  * rocm_wmma_gemm/config/generate_config.py:94-103).
  *   tile_m   rows of C per CTA (per CTA pair when cluster == 2): 128, or 256 with cluster 2
- *   tile_n   columns of C per CTA / CTA pair: 64, 128 or 256
+ *   tile_n   columns of C per CTA / CTA pair: 64, 128, 256, or 512 (512: cluster 2 only)
  *   stages   depth of the TMA -> shared-memory ring (2 .. 8, clamped to what fits)
  *   cluster  1 = one CTA per tile, 2 = a CTA pair shares one tile (cta_group::2 MMA)
  *   split_k  number of K partitions reduced through an f32 workspace (1 = none)

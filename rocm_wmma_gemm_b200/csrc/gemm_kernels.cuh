@@ -195,7 +195,7 @@ __device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits)
 //                      for a pair it lives in rank 0 and counts both CTAs' bytes) and an
 //                      `empty` barrier (MMAs that read the slot have retired).
 //   warp 1 (one lane)  MMA issuer (rank 0 only for a pair): 4 x tcgen05.mma per slot into one
-//                      of two TMEM accumulators (BN f32 columns each); tcgen05.commit releases
+//                      of the TMEM accumulators (BN f32 columns each); tcgen05.commit releases
 //                      the slot and, after the last k-block, publishes the accumulator.
 //   warps 2..5         epilogue: tcgen05.ld 32 lanes x 32 columns, convert, swizzled store to a
 //                      per-warp staging buffer, TMA store of 32 rows x 128 B; the accumulator
@@ -211,16 +211,25 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                      const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmD, const GemmParams p)
 {
-    static_assert(BN == 64 || BN == 128 || BN == 256, "BN must be 64, 128 or 256");
+    static_assert(BN == 64 || BN == 128 || BN == 256 || BN == 512, "BN must be 64, 128, 256 or 512");
     static_assert(CL == 1 || CL == 2, "cluster size must be 1 or 2");
-    constexpr int      BN_CTA       = BN / CL; // B' rows this CTA stages
+    // One MMA covers at most 256 columns: a 512-wide tile is two sub-tiles that share the A'
+    // operand of every K slice (A' is staged once for 512 columns of output).
+    constexpr int      UMMA_N       = BN > 256 ? 256 : BN;
+    constexpr int      NSUB         = BN / UMMA_N;
+    constexpr int      SUB_ROWS     = UMMA_N / CL;          // B' rows per sub-tile in this CTA
+    constexpr int      BN_CTA       = NSUB * SUB_ROWS;      // B' rows this CTA stages
+    constexpr uint32_t SUB_BYTES    = SUB_ROWS * BLOCK_K * 2;
     constexpr uint32_t B_TILE_BYTES = BN_CTA * BLOCK_K * 2;
     constexpr uint32_t STAGE_BYTES  = A_TILE_BYTES + B_TILE_BYTES;
-    constexpr uint32_t TMEM_COLS    = 2 * BN; // two accumulators; power of two >= 32
+    // TMEM holds 512 f32 columns: two accumulators (epilogue of tile i overlaps the main loop
+    // of tile i + 1) up to BN = 256, a single one for BN = 512.
+    constexpr uint32_t NUM_ACC      = BN > 256 ? 1 : 2;
+    constexpr uint32_t TMEM_COLS    = NUM_ACC * BN; // power of two >= 32
     constexpr int      OUT_BYTES    = (OUT == OUT_F32) ? 4 : 2;
     constexpr int      CH           = 128 / OUT_BYTES; // output columns per 128-byte chunk
     constexpr int      NCHUNK       = BN / CH;
-    static_assert(BN_CTA >= 64, "each CTA stages at least 64 rows of B'");
+    static_assert(SUB_ROWS >= 64, "each CTA stages at least 64 rows of B' per sub-tile");
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t s_full[MAX_STAGES];
@@ -278,7 +287,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             for (uint32_t w = unit; ok && w < p.num_work; w += units) {
                 const WorkCoord c  = decode_work(p, w, BN, BLOCK_M * CL);
                 const int32_t   am = static_cast<int32_t>(c.m0 + rank * BLOCK_M);
-                const int32_t   bn = static_cast<int32_t>(c.n0 + rank * BN_CTA);
+                const int32_t   bn = static_cast<int32_t>(c.n0 + rank * SUB_ROWS);
                 for (uint32_t kb = c.kb0; kb < c.kb1; ++kb) {
                     ok = bounded_wait(ptx::smem_u32(&s_empty[stage]), phase ^ 1u, &s_abort,
                                       p.status, ST_PRODUCER_WAIT);
@@ -302,13 +311,18 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                             tma_load<CL>(sa + j * (64 * BLOCK_K * 2), &tmA, bar, am + j * 64, k0,
                                          c.z_in);
                     }
-                    if (p.b_mn_major == 0u) {
-                        tma_load<CL>(sb, &tmB, bar, k0, bn, c.z_in);
-                    } else {
 #pragma unroll
-                        for (int j = 0; j < BN_CTA / 64; ++j)
-                            tma_load<CL>(sb + j * (64 * BLOCK_K * 2), &tmB, bar, bn + j * 64, k0,
-                                         c.z_in);
+                    for (int h = 0; h < NSUB; ++h) {
+                        const int32_t  bh = bn + h * UMMA_N; // first B' row of sub-tile h
+                        const uint32_t sh = sb + h * SUB_BYTES;
+                        if (p.b_mn_major == 0u) {
+                            tma_load<CL>(sh, &tmB, bar, k0, bh, c.z_in);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < SUB_ROWS / 64; ++j)
+                                tma_load<CL>(sh + j * (64 * BLOCK_K * 2), &tmB, bar, bh + j * 64,
+                                             k0, c.z_in);
+                        }
                     }
                     ++issued;
                     if (++stage == stages) {
@@ -349,8 +363,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             bool           ok = true;
             for (uint32_t w = unit; ok && w < p.num_work; w += units, ++it) {
                 const WorkCoord c      = decode_work(p, w, BN, BLOCK_M * CL);
-                const uint32_t  buf    = it & 1u;
-                const uint32_t  aphase = (it >> 1) & 1u;
+                const uint32_t  buf    = it % NUM_ACC;
+                const uint32_t  aphase = (it / NUM_ACC) & 1u;
                 ok = bounded_wait<CL == 2>(ptx::smem_u32(&s_tempty[buf]), aphase ^ 1u, &s_abort,
                                            p.status, ST_MMA_WAIT_ACC);
                 if (!ok) break;
@@ -367,8 +381,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     const uint64_t bd = ptx::make_smem_desc(sb, b_lbo, 1024u);
 #pragma unroll
                     for (uint32_t k = 0; k < BLOCK_K / UMMA_K; ++k) {
-                        ptx::umma_f16<CL>(d_tmem, ad + k * a_kstep, bd + k * b_kstep, p.idesc,
-                                          (kb > c.kb0 || k > 0u) ? 1u : 0u);
+#pragma unroll
+                        for (uint32_t h = 0; h < NSUB; ++h) {
+                            ptx::umma_f16<CL>(d_tmem + h * UMMA_N, ad + k * a_kstep,
+                                              bd + h * (SUB_BYTES >> 4) + k * b_kstep, p.idesc,
+                                              (kb > c.kb0 || k > 0u) ? 1u : 0u);
+                        }
                     }
                     // Slot free (in both CTAs of a pair) once these MMAs retire.
                     umma_arrive<CL>(ptx::smem_u32(&s_empty[stage]));
@@ -399,8 +417,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         bool           ok   = true;
         for (uint32_t w = unit; ok && w < p.num_work; w += units, ++it) {
             const WorkCoord c      = decode_work(p, w, BN, BLOCK_M * CL);
-            const uint32_t  buf    = it & 1u;
-            const uint32_t  aphase = (it >> 1) & 1u;
+            const uint32_t  buf    = it % NUM_ACC;
+            const uint32_t  aphase = (it / NUM_ACC) & 1u;
             ok = bounded_wait(ptx::smem_u32(&s_tfull[buf]), aphase, &s_abort, p.status,
                               ST_EPI_WAIT);
             ok = __all_sync(0xffffffffu, ok); // warp-uniform: the TMEM loads below are aligned

@@ -151,7 +151,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 struct DeviceCtx {
     bool          ready    = false;
     int           sm_count = 0;
-    int           pair_units[2] = {0, 0}; // co-resident CTA pairs for tile_n 128 / 256 (0 = not asked yet)
+    int           pair_units[3] = {0, 0, 0}; // co-resident CTA pairs for tile_n 128 / 256 / 512 (0 = not asked yet)
     unsigned int* d_status = nullptr;
     // host-buffer path
     cudaStream_t h_stream = nullptr;
@@ -218,6 +218,7 @@ static int get_ctx(DeviceCtx** out)
         CUDA_TRY((set_smem_attr<256, 1>()));
         CUDA_TRY((set_smem_attr<128, 2>()));
         CUDA_TRY((set_smem_attr<256, 2>()));
+        CUDA_TRY((set_smem_attr<512, 2>()));
         c.ready = true;
     }
     *out = &c;
@@ -320,9 +321,10 @@ static int check_config(const b200_gemm_config& c)
     if (c.cluster != 1 && c.cluster != 2) return fail(B200_GEMM_ERR_BAD_CONFIG, "cluster %d not compiled (1 or 2)", c.cluster);
     if (c.tile_m != 128 * c.cluster)
         return fail(B200_GEMM_ERR_BAD_CONFIG, "tile_m %d does not match cluster %d (tile_m = 128 * cluster)", c.tile_m, c.cluster);
-    if (c.tile_n != 64 && c.tile_n != 128 && c.tile_n != 256)
-        return fail(B200_GEMM_ERR_BAD_CONFIG, "tile_n %d not compiled (64, 128, 256)", c.tile_n);
+    if (c.tile_n != 64 && c.tile_n != 128 && c.tile_n != 256 && c.tile_n != 512)
+        return fail(B200_GEMM_ERR_BAD_CONFIG, "tile_n %d not compiled (64, 128, 256, 512)", c.tile_n);
     if (c.cluster == 2 && c.tile_n == 64) return fail(B200_GEMM_ERR_BAD_CONFIG, "tile_n 64 needs cluster 1");
+    if (c.cluster == 1 && c.tile_n == 512) return fail(B200_GEMM_ERR_BAD_CONFIG, "tile_n 512 needs cluster 2");
     if (c.stages < 2 || c.stages > MAX_STAGES) return fail(B200_GEMM_ERR_BAD_CONFIG, "stages %d outside 2..%d", c.stages, MAX_STAGES);
     if (c.split_k < 1 || c.split_k > 64) return fail(B200_GEMM_ERR_BAD_CONFIG, "split_k %d outside 1..64", c.split_k);
     if (c.raster < 0 || c.raster > 64) return fail(B200_GEMM_ERR_BAD_CONFIG, "raster %d outside 0..64", c.raster);
@@ -530,13 +532,14 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     const uint64_t work = (uint64_t)gp.batch * split * gp.m_tiles * gp.n_tiles;
     if (work > 0x7fffffffull) return fail(B200_GEMM_ERR_BAD_SIZE, "too many tiles (%llu)", (unsigned long long)work);
     gp.num_work   = (uint32_t)work;
+    const int umma_n = bn > 256 ? 256 : bn; // columns per MMA; a 512-wide tile is two sub-tiles
     gp.a_mn_major = v.a_mn ? 1u : 0u;
     gp.b_mn_major = v.b_mn ? 1u : 0u;
     // tcgen05 instruction descriptor, kind::f16: [4,6) D format (1 = f32); [7,10) A format and
     // [10,13) B format (0 = f16, 1 = bf16); bit 15 / 16: A / B is MN-major; [17,23) N >> 3;
     // [24,29) M >> 4 (M = 256 for a CTA pair).
     gp.idesc = (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | (gp.a_mn_major << 15) |
-               (gp.b_mn_major << 16) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)((BLOCK_M * cl) >> 4) << 24);
+               (gp.b_mn_major << 16) | ((uint32_t)(umma_n >> 3) << 17) | ((uint32_t)((BLOCK_M * cl) >> 4) << 24);
     gp.stages = (uint32_t)cfg.stages;
     gp.status = ctx->d_status;
 
@@ -550,7 +553,7 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
 
     CUtensorMap tmA, tmB, tmD;
     st = encode_operand(&tmA, bf16, v.a, v.M, v.K, p.batch, v.a_mn, BLOCK_M);
-    if (st == B200_GEMM_OK) st = encode_operand(&tmB, bf16, v.b, v.N, v.K, p.batch, v.b_mn, (uint32_t)bn / cl);
+    if (st == B200_GEMM_OK) st = encode_operand(&tmB, bf16, v.b, v.N, v.K, p.batch, v.b_mn, (uint32_t)umma_n / cl);
     if (st == B200_GEMM_OK) {
         if (split > 1)
             st = encode_map(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ws, v.N, v.M, (uint64_t)p.batch * split, 32, 32);
@@ -571,7 +574,8 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     cudaError_t    e;
     if (cl == 2) {
         if (bn == 128) e = launch_bn<128, 2>(kern_out, units, &ctx->pair_units[0], smem, stream, tmA, tmB, tmD, gp);
-        else e = launch_bn<256, 2>(kern_out, units, &ctx->pair_units[1], smem, stream, tmA, tmB, tmD, gp);
+        else if (bn == 256) e = launch_bn<256, 2>(kern_out, units, &ctx->pair_units[1], smem, stream, tmA, tmB, tmD, gp);
+        else e = launch_bn<512, 2>(kern_out, units, &ctx->pair_units[2], smem, stream, tmA, tmB, tmD, gp);
     } else {
         switch (bn) {
             case 64: e = launch_bn<64, 1>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;

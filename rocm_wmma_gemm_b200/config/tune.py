@@ -1,0 +1,309 @@
+#!/usr/bin/env python
+"""GOMEA tuner for the B200 GEMM kernels.
+
+Counterpart of the reference's rocm_wmma_gemm/config/tune.py: for every (M, N, K) x layout it
+searches the launch-configuration space with parameter-less GOMEA (gomea.py) and writes a JSON
+table in the reference's schema
+    {"configurations": [{"range": {M, N, K}, "layout": {A, B, C}, "config": {...}}]}
+whose `config` object carries the B200 keys {tile_m, tile_n, stages, cluster, split_k, raster}.
+generate_config.py turns the table into the compiled lookup.
+
+What changed against the reference, and why:
+  * one evaluation is an in-process timing through the library's C ABI (`b200_gemm_ex` with an
+    explicit config, CUDA events) instead of a freshly spawned process that compiles one
+    kernel: every variant is precompiled, so an evaluation costs milliseconds.
+    `--evaluator subprocess` keeps the reference's process-per-evaluation flow through the
+    `tuner` binary (config/tuner.cpp).
+  * the parameter space and the constraints are the sm_100a ones (shared memory per ring
+    slot, TMEM columns, CTA pairs) instead of warps x warp tiles x LDS.
+  * the table is flushed after every (size, layout), so an interrupted run resumes with
+    `--input <same file>`.
+  * winners are re-timed interleaved with the runners-up before they are written, because
+    B200 clocks move with the power cap from one second to the next.
+"""
+from __future__ import annotations
+
+import argparse
+import itertools
+import json
+import os
+import random
+import re
+import statistics
+import subprocess
+import sys
+import time
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+
+from rocm_wmma_gemm_b200.config.gomea import INF, Gomea  # noqa: E402
+
+PARAMS = ["tile_m", "tile_n", "stages", "split_k", "raster"]
+SPACE = {
+    "tile_m": [128, 256],
+    "tile_n": [64, 128, 256, 512],
+    "stages": [2, 3, 4, 5, 6, 8],
+    "split_k": [1, 2, 3, 4, 6, 8, 12, 16, 24, 32],
+    "raster": [0, 1, 2, 4, 8, 16, 32],
+}
+SMEM_LIMIT = 232448          # bytes a CTA may use
+EPILOGUE_BYTES = 4 * 2 * 4096  # per-warp double-buffered store staging
+WORKSPACE_LIMIT = 4 << 30    # split-K partials the tuner is willing to allocate
+
+DEFAULT_SIZES = [
+    # the reference's tuned set (tune.py:885-890) ...
+    (1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (8192, 8192, 8192), (4096, 4096, 1024),
+    (8192, 8192, 1024), (4096, 2048, 64), (8192, 4096, 128), (4096, 16384, 4096), (4096, 4096, 16384),
+    (2048, 5120, 5120), (4096, 5120, 5120), (32768, 4096, 4096), (65536, 2048, 2048),
+    # ... plus the target shapes: projections, skinny, large and their column slabs
+    (4096, 4096, 2048), (8192, 28672, 8192), (8192, 8192, 28672),
+    (16, 8192, 8192), (64, 8192, 8192), (128, 8192, 8192), (16, 28672, 8192), (64, 28672, 8192), (128, 28672, 8192),
+    (16384, 16384, 16384), (16384, 8192, 16384), (16384, 4096, 16384), (16384, 2048, 16384),
+]
+ALL_LAYOUTS = [(0, 0, 0), (0, 1, 0), (1, 0, 0), (1, 1, 0), (0, 0, 1), (0, 1, 1), (1, 0, 1), (1, 1, 1)]  # row-major C first
+LAYOUT_NAME = {0: "row_major", 1: "col_major"}
+TYPE_INDEX = {"f16_f16": 0, "f32_f16": 1, "bf16_bf16": 2, "f32_bf16": 3}
+
+
+def cluster_of(tile_m: int) -> int:
+    return tile_m // 128
+
+
+def stage_bytes(tile_n: int, cluster: int) -> int:
+    return 128 * 64 * 2 + (tile_n // cluster) * 64 * 2
+
+
+def max_stages(tile_n: int, cluster: int) -> int:
+    return min(8, (SMEM_LIMIT - 512 - EPILOGUE_BYTES - 1024) // stage_bytes(tile_n, cluster))
+
+
+def check_constraints(cfg, M=None, N=None, K=None, lc=0) -> bool:
+    """Hardware and problem constraints of one configuration (tuple in PARAMS order)."""
+    tile_m, tile_n, stages, split_k, raster = cfg
+    cl = cluster_of(tile_m)
+    if cl == 1 and tile_n > 256:
+        return False                      # one CTA holds two accumulators: 2 * tile_n <= 512 TMEM columns
+    if cl == 2 and tile_n < 128:
+        return False                      # each CTA of a pair stages >= 64 rows of B
+    if stages > max_stages(tile_n, cl):
+        return False                      # ring + epilogue staging must fit 227 KiB
+    if K is not None:
+        k_blocks = (K + 63) // 64
+        if split_k > k_blocks:
+            return False
+        per = -(-k_blocks // split_k)
+        if -(-k_blocks // per) != split_k:
+            return False                  # would be legalised to a smaller split: skip the duplicate
+        if split_k > 1 and M is not None and split_k * M * N * 4 > WORKSPACE_LIMIT:
+            return False
+    if M is not None:
+        mk, nk = (M, N) if lc == 0 else (N, M)   # kernel view: column-major C swaps the roles
+        m_tiles = -(-mk // tile_m)
+        if raster > max(1, m_tiles) and raster not in (0, 1):
+            return False                  # bands taller than the matrix are all the same sweep
+    return True
+
+
+def enumerate_valid(M, N, K, lc):
+    return [c for c in itertools.product(*[SPACE[p] for p in PARAMS]) if check_constraints(c, M, N, K, lc)]
+
+
+def to_dict(cfg) -> dict:
+    d = dict(zip(PARAMS, cfg))
+    d["cluster"] = cluster_of(d["tile_m"])
+    return {k: d[k] for k in ("tile_m", "tile_n", "stages", "cluster", "split_k", "raster")}
+
+
+def from_dict(d) -> tuple:
+    return tuple(int(d[p]) for p in PARAMS)
+
+
+# ---------------------------------------------------------------------------------------------
+# Evaluators
+# ---------------------------------------------------------------------------------------------
+class InProcessEvaluator:
+    """Times `b200_gemm_ex` with an explicit config on the current device."""
+
+    def __init__(self, type_str: str, warmup: int = 2, iters: int = 6, reps: int = 3):
+        import torch
+        import rocm_wmma_gemm_b200 as g
+        self.torch, self.g = torch, g
+        self.types = TYPE_INDEX[type_str]
+        self.loader = g.loader()
+        self.warmup, self.iters, self.reps = warmup, iters, reps
+        self.shape = None
+
+    def prepare(self, M, N, K):
+        if self.shape == (M, N, K):
+            return
+        torch = self.torch
+        in_dt = torch.bfloat16 if self.types >= 2 else torch.float16
+        out_dt = torch.float32 if self.types in (1, 3) else in_dt
+        # the reference tuner's five-value cyclic fill (config/tuner.cpp:107-122)
+        vals = torch.tensor([0.1, 0.125, 0.15, 0.175, 0.2], device="cuda")
+        self.A = vals[torch.arange(M * K, device="cuda") % 5].to(in_dt)
+        self.B = vals[torch.arange(K * N, device="cuda") % 5].to(in_dt)
+        self.C = torch.empty(M * N, device="cuda", dtype=out_dt)
+        self.shape = (M, N, K)
+        self.e0 = torch.cuda.Event(enable_timing=True)
+        self.e1 = torch.cuda.Event(enable_timing=True)
+
+    def _batch(self, M, N, K, la, lb, lc, cfg, iters):
+        self.e0.record()
+        for _ in range(iters):
+            self.loader.gemm(self.C, self.A, self.B, M, N, K, lc, la, lb, types=self.types, config=cfg)
+        self.e1.record()
+        self.torch.cuda.synchronize()
+        return self.e0.elapsed_time(self.e1) / iters
+
+    def __call__(self, M, N, K, la, lb, lc, cfg_tuple) -> float:
+        self.prepare(M, N, K)
+        d = to_dict(cfg_tuple)
+        cfg = self.g.GemmConfig(d["tile_m"], d["tile_n"], d["stages"], d["cluster"], d["split_k"], d["raster"])
+        try:
+            t1 = self._batch(M, N, K, la, lb, lc, cfg, self.warmup)
+            # long kernels need fewer repetitions for a stable number: ~4 ms per timed batch
+            iters = max(1, min(self.iters, int(4.0 / max(t1, 1e-3))))
+            return statistics.median(self._batch(M, N, K, la, lb, lc, cfg, iters) for _ in range(self.reps))
+        except self.g.GemmError:
+            return INF
+
+
+class SubprocessEvaluator:
+    """One `tuner` process per evaluation, parsed from its `manual_time` line (the reference's
+    flow, rocm_wmma_gemm/config/tune.py:150-180)."""
+
+    def __init__(self, type_str: str, binary: str):
+        self.type_str, self.binary = type_str, binary
+
+    def __call__(self, M, N, K, la, lb, lc, cfg_tuple) -> float:
+        d = to_dict(cfg_tuple)
+        argv = [self.binary, str(M), str(N), str(K), str(d["tile_m"]), str(d["tile_n"]), str(d["stages"]),
+                str(d["cluster"]), str(d["split_k"]), str(d["raster"]), str(la), str(lb), str(lc), "sm_100a", self.type_str]
+        try:
+            out = subprocess.run(argv, capture_output=True, text=True, timeout=60, check=False)
+        except Exception:
+            return INF
+        if out.returncode != 0:
+            return INF
+        m = re.search(r"manual_time\s+([0-9.]+)\s+ms", out.stdout)
+        return float(m.group(1)) if m else INF
+
+
+# ---------------------------------------------------------------------------------------------
+# Tuning loop
+# ---------------------------------------------------------------------------------------------
+def load_table(path):
+    """{(M,N,K): {(la,lb,lc): entry}} from a JSON table (missing file -> empty)."""
+    table = {}
+    if not path or not os.path.exists(path):
+        return table
+    with open(path) as f:
+        data = json.load(f)
+    inv = {"row_major": 0, "col_major": 1}
+    for e in data.get("configurations", []):
+        r, l = e["range"], e["layout"]
+        table.setdefault((r["M"], r["N"], r["K"]), {})[(inv[l["A"]], inv[l["B"]], inv[l["C"]])] = e
+    return table
+
+
+def save_table(path, table):
+    entries = [table[s][l] for s in sorted(table) for l in sorted(table[s])]
+    tmp = path + ".tmp"
+    with open(tmp, "w") as f:
+        json.dump({"configurations": entries}, f, indent=1)
+    os.replace(tmp, path)
+
+
+def refine(evaluate, shape, layout, candidates, rounds=3):
+    """Interleaved re-timing of the finalists; returns (best config, its median time)."""
+    times = {c: [] for c in candidates}
+    for _ in range(rounds):
+        for c in candidates:
+            times[c].append(evaluate(*shape, *layout, c))
+    med = {c: statistics.median(t) for c, t in times.items()}
+    best = min(med, key=med.get)
+    return best, med[best]
+
+
+def tune_layout(evaluate, shape, layout, budget, seeds, rng, log):
+    M, N, K = shape
+    la, lb, lc = layout
+    valid = enumerate_valid(M, N, K, lc)
+    search = Gomea(valid, lambda c: evaluate(M, N, K, la, lb, lc, c), budget, seeds=seeds,
+                   strata=lambda c: c[0] * c[1], rng=rng, log=log)
+    res = search.run()
+    finalists = [c for _, c in res.elites[:3]]
+    if res.best is not None and res.best not in finalists:
+        finalists.insert(0, res.best)
+    if not finalists:
+        return None
+    best, t = refine(evaluate, shape, layout, finalists)
+    return {"config": best, "time_ms": t, "evaluations": res.evaluations}
+
+
+def main(argv=None):
+    p = argparse.ArgumentParser(description="B200 GEMM tuner (parameter-less GOMEA)")
+    p.add_argument("--input", "-i", help="existing JSON table: its entries seed the search and are kept")
+    p.add_argument("--output", "-o", help="output JSON (default: gemm_config_sm100_<f16|f32>.json beside this file)")
+    p.add_argument("--sizes", nargs="*", help="M,N,K ...")
+    p.add_argument("--layouts", nargs="*", help="A,B,C as r/c letters or 0/1, e.g. r,c,r")
+    p.add_argument("--budget", type=int, default=48, help="evaluations for the first layout of a size")
+    p.add_argument("--budget-seeded", type=int, default=16, help="evaluations for layouts seeded by earlier winners")
+    p.add_argument("--seed", type=int, default=42)
+    p.add_argument("--type", default="bf16_bf16", choices=list(TYPE_INDEX))
+    p.add_argument("--overwrite", action="store_true", help="re-tune entries the input already has")
+    p.add_argument("--evaluator", default="inprocess", choices=["inprocess", "subprocess"])
+    p.add_argument("--tuner-binary", default=os.path.join(HERE, "tuner"))
+    p.add_argument("--max-seconds", type=float, default=0, help="stop after this long (0 = no limit); the table is saved as it grows")
+    args = p.parse_args(argv)
+
+    group = "f32" if args.type in ("f32_f16", "f32_bf16") else "f16"
+    out = args.output or os.path.join(HERE, f"gemm_config_sm100_{group}.json")
+    table = load_table(args.input or out)
+    sizes = [tuple(int(x) for x in s.split(",")) for s in args.sizes] if args.sizes else DEFAULT_SIZES
+
+    def lay(tok):
+        return tuple({"r": 0, "c": 1, "0": 0, "1": 1}[x] for x in tok.split(","))
+    layouts = [lay(t) for t in args.layouts] if args.layouts else ALL_LAYOUTS
+    layouts = sorted(layouts, key=lambda l: l[2])  # row-major C first: its winners seed column-major C
+
+    evaluate = InProcessEvaluator(args.type) if args.evaluator == "inprocess" else SubprocessEvaluator(args.type, args.tuner_binary)
+    rng = random.Random(args.seed)
+    t_start = time.time()
+    for shape in sizes:
+        winners = []
+        for layout in layouts:
+            if args.max_seconds and time.time() - t_start > args.max_seconds:
+                print("time limit reached; table saved to", out)
+                return 0
+            have = table.get(shape, {}).get(layout)
+            seeds = list(winners)
+            if have is not None:
+                if not args.overwrite:
+                    winners.append(from_dict(have["config"]))
+                    continue
+                seeds.insert(0, from_dict(have["config"]))
+            budget = args.budget if not winners else args.budget_seeded
+            r = tune_layout(evaluate, shape, layout, budget, seeds, rng, lambda s: None)
+            if r is None:
+                print(f"{shape} {layout}: no valid configuration ran")
+                continue
+            winners.append(r["config"])
+            M, N, K = shape
+            tflops = 2.0 * M * N * K / (r["time_ms"] * 1e-3) / 1e12
+            entry = {"range": {"M": M, "N": N, "K": K},
+                     "layout": {"A": LAYOUT_NAME[layout[0]], "B": LAYOUT_NAME[layout[1]], "C": LAYOUT_NAME[layout[2]]},
+                     "config": to_dict(r["config"]), "time_ms": round(r["time_ms"], 5), "tflops": round(tflops, 1),
+                     "evaluations": r["evaluations"], "type": args.type}
+            table.setdefault(shape, {})[layout] = entry
+            save_table(out, table)  # resume point
+            print(f"{M}x{N}x{K} A={'rc'[layout[0]]} B={'rc'[layout[1]]} C={'rc'[layout[2]]}: {to_dict(r['config'])} "
+                  f"{r['time_ms']:.4f} ms {tflops:.0f} TFLOP/s ({r['evaluations']} evals)", flush=True)
+    print("saved", out)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -426,23 +426,30 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             ptx::tc_fence_after();
             const uint32_t row0     = c.m0 + rank * BLOCK_M + q * 32u;
             const bool     row_live = row0 < p.M;
+            // Software pipeline over 128-byte column chunks: the TMEM load of chunk ch + 1 is
+            // in flight while chunk ch is converted, staged and handed to the TMA store.
+            const uint32_t tacc = tmem_base + ((q * 32u) << 16) + buf * BN;
+            uint32_t       n0[32], n1[32]; // raw accumulator words of the chunk in flight
+            ptx::tmem_ld_32x32(tacc, n0);
+            if constexpr (OUT != OUT_F32) ptx::tmem_ld_32x32(tacc + 32u, n1);
 #pragma unroll 1
             for (int ch = 0; ch < NCHUNK; ++ch) {
-                const uint32_t taddr = tmem_base + ((q * 32u) << 16) + buf * BN + ch * CH;
-                uint32_t       v[32];
+                uint32_t v[32];
+                ptx::tmem_ld_wait(n0);
                 if constexpr (OUT == OUT_F32) {
-                    ptx::tmem_ld_32x32(taddr, v);
-                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = n0[j];
                 } else {
-                    uint32_t lo[32], hi[32];
-                    ptx::tmem_ld_32x32(taddr, lo);
-                    ptx::tmem_ld_32x32(taddr + 32u, hi);
-                    ptx::tmem_ld_wait();
+                    ptx::tmem_ld_wait(n1);
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        v[j]      = pack2<OUT>(lo[2 * j], lo[2 * j + 1]);
-                        v[16 + j] = pack2<OUT>(hi[2 * j], hi[2 * j + 1]);
+                        v[j]      = pack2<OUT>(n0[2 * j], n0[2 * j + 1]);
+                        v[16 + j] = pack2<OUT>(n1[2 * j], n1[2 * j + 1]);
                     }
+                }
+                if (ch + 1 < NCHUNK) {
+                    ptx::tmem_ld_32x32(tacc + (ch + 1) * CH, n0);
+                    if constexpr (OUT != OUT_F32) ptx::tmem_ld_32x32(tacc + (ch + 1) * CH + 32u, n1);
                 }
                 if (ch == NCHUNK - 1) {
                     // Accumulator fully read: hand it back to the MMA issuer (rank 0).

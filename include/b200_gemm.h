@@ -141,6 +141,35 @@ size_t b200_gemm_workspace_bytes(int types, size_t M, size_t N, size_t K, size_t
                                  int layout_c, int layout_a, int layout_b,
                                  const b200_gemm_config* cfg);
 
+/* Bytes of the built-in split-K workspace used by b200_gemm_splitk_static. */
+#define B200_GEMM_STATIC_WORKSPACE_BYTES (16u << 20)
+
+/* C = A*B like b200_gemm_ex, for callers that must not allocate device memory while they run:
+ * a server whose device memory was partitioned once at start-up, a latency-critical thread
+ * that may not wait on the driver's allocator, a plugin inside a framework that owns all
+ * allocations.  This entry point never calls cudaMalloc, cudaFree, their stream-ordered forms
+ * or any allocating library routine.  Where the chosen configuration splits K, the f32
+ * partial results go to a workspace that is part of the library image
+ * (B200_GEMM_STATIC_WORKSPACE_BYTES on every GPU that loads the library, held until the
+ * process exits) instead of a freshly allocated one.
+ *   - A request whose partials (batch_count x split_k x M x N x 4 bytes) exceed the workspace
+ *     is refused with B200_GEMM_ERR_TOO_LARGE; nothing runs.  Shapes the tensor-copy engine
+ *     cannot address (pointers not 16-byte aligned, contiguous extents not multiples of 8
+ *     elements) are refused with B200_GEMM_ERR_MISALIGNED, and K == 0 with BAD_SIZE.
+ *   - The first call on each device looks up the workspace's device address and sets kernel
+ *     attributes; make that first call once per device before any stream capture begins.
+ *   - All calls on a device share the one workspace and it keeps whatever the previous call
+ *     left there.  Nothing in it needs to start at zero (every partial is fully overwritten
+ *     before it is read), but two calls that overlap on the GPU — different streams, or
+ *     different threads — race on it: serialise them on one stream or with events.
+ *   - Failures of device-side waits are recorded in a status word of this entry point's own,
+ *     not the one b200_gemm_device_status reads.
+ * cfg == NULL lets the tuned table choose.  This entry point has no counterpart in the
+ * reference library, which never uses scratch memory. */
+int b200_gemm_splitk_static(int types, void* C, const void* A, const void* B, size_t M, size_t N,
+                            size_t K, size_t batch_count, int layout_c, int layout_a, int layout_b,
+                            void* stream, const b200_gemm_config* cfg);
+
 /* Synchronises the current device and returns B200_GEMM_ERR_DEVICE_WAIT if any kernel of
  * this library has given up on a bounded wait since the last call (then clears the flag),
  * else B200_GEMM_OK.  `detail`, if not NULL, receives the raw device status word. */

@@ -622,6 +622,179 @@ static int run_from_abi(int types, void* C, const void* A, const void* B, size_t
     }
 }
 
+
+// ------------------------------------------------------------------------------------------
+// Split-K GEMM that allocates nothing
+// ------------------------------------------------------------------------------------------
+// Some host programs must not allocate device memory on the call path: a serving loop whose
+// memory was carved up once at start-up and is accounted to the last byte, a real-time thread
+// that may not enter the driver's allocator (it can block on other threads' allocations), or a
+// plugin running inside a framework that owns the allocator.  For them the f32 split-K
+// partials and the device status word live in the two file-scope arrays below, which every
+// GPU that loads the library holds from load to exit.
+//
+// g_static_workspace / g_static_status name host-side stand-ins for the device arrays; the
+// device addresses come from cudaGetSymbolAddress, asked once per device with that device
+// current, and only those are handed to kernels and TMA descriptors.
+static __device__ __align__(256) float        g_static_workspace[B200_GEMM_STATIC_WORKSPACE_BYTES / sizeof(float)];
+static __device__ __align__(256) unsigned int g_static_status[64];
+
+struct StaticCtx {
+    bool          ready    = false;
+    int           sm_count = 0;
+    float*        d_ws     = nullptr; // device address of g_static_workspace on this device
+    unsigned int* d_status = nullptr; // device address of g_static_status on this device
+    int           pair_units[3] = {0, 0, 0};
+};
+static StaticCtx g_static_ctx[k_max_devices];
+
+// First call on a device: resolves the arrays' device addresses and sets the kernels'
+// shared-memory attributes.  Allocates nothing.
+static int get_static_ctx(StaticCtx** out)
+{
+    int         dev = -1;
+    cudaError_t e   = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(B200_GEMM_ERR_NO_DEVICE, "no CUDA device: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= k_max_devices) return fail(B200_GEMM_ERR_NO_DEVICE, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    StaticCtx&                  c = g_static_ctx[dev];
+    if (!c.ready) {
+        cudaDeviceProp prop;
+        CUDA_TRY(cudaGetDeviceProperties(&prop, dev));
+        if (prop.major != 10)
+            return fail(B200_GEMM_ERR_NO_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only", dev,
+                        prop.major, prop.minor);
+        c.sm_count = prop.multiProcessorCount;
+        if (!g_encode) {
+            void*                           fn = nullptr;
+            cudaDriverEntryPointQueryResult qr;
+            CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr));
+            if (!fn || qr != cudaDriverEntryPointSuccess)
+                return fail(B200_GEMM_ERR_CUDA, "cuTensorMapEncodeTiled not available");
+            g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+        }
+        CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&c.d_ws), g_static_workspace));
+        CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&c.d_status), g_static_status));
+        CUDA_TRY((set_smem_attr<64, 1>()));
+        CUDA_TRY((set_smem_attr<128, 1>()));
+        CUDA_TRY((set_smem_attr<256, 1>()));
+        CUDA_TRY((set_smem_attr<128, 2>()));
+        CUDA_TRY((set_smem_attr<256, 2>()));
+        CUDA_TRY((set_smem_attr<512, 2>()));
+        c.ready = true;
+    }
+    *out = &c;
+    return B200_GEMM_OK;
+}
+
+static int run_gemm_static(const Problem& p, cudaStream_t stream, const b200_gemm_config* user_cfg)
+{
+    int st = validate(p);
+    if (st != B200_GEMM_OK) return st;
+    if (p.M == 0 || p.N == 0) return B200_GEMM_OK;
+    if (p.K == 0) return fail(B200_GEMM_ERR_BAD_SIZE, "K == 0 is not handled by the allocation-free entry point");
+
+    StaticCtx* ctx = nullptr;
+    st             = get_static_ctx(&ctx);
+    if (st != B200_GEMM_OK) return st;
+
+    const View v = make_view(p);
+    if (!tma_ok(p, v))
+        return fail(B200_GEMM_ERR_MISALIGNED,
+                    "the allocation-free entry point needs 16-byte aligned pointers and contiguous extents that are "
+                    "multiples of 8 elements (M=%zu N=%zu K=%zu)", p.M, p.N, p.K);
+
+    b200_gemm_config cfg = resolve_config(p, user_cfg, nullptr);
+    st                   = check_config(cfg);
+    if (st != B200_GEMM_OK) return st;
+    uint32_t kb_per_split = 0;
+    legalize(cfg, v, &kb_per_split);
+
+    const int      bn    = cfg.tile_n;
+    const int      out   = out_kind(p.types);
+    const bool     bf16  = in_is_bf16(p.types);
+    const uint32_t split = (uint32_t)cfg.split_k;
+    const uint32_t cl    = (uint32_t)cfg.cluster;
+
+    const size_t ws_bytes = split > 1 ? (size_t)p.batch * split * v.M * v.N * sizeof(float) : 0;
+    if (ws_bytes > (size_t)B200_GEMM_STATIC_WORKSPACE_BYTES)
+        return fail(B200_GEMM_ERR_TOO_LARGE,
+                    "split-K partials need %zu bytes (batch %zu x split %u x %u x %u x 4) but the built-in workspace "
+                    "holds %zu; use fewer partitions or the allocating entry points",
+                    ws_bytes, p.batch, split, v.M, v.N, (size_t)B200_GEMM_STATIC_WORKSPACE_BYTES);
+    if (split > 1 && v.N % 4) return fail(B200_GEMM_ERR_BAD_CONFIG, "split_k needs N %% 4 == 0 in the kernel view");
+
+    GemmParams gp;
+    gp.M            = v.M;
+    gp.N            = v.N;
+    gp.K            = v.K;
+    gp.batch        = (uint32_t)p.batch;
+    gp.m_tiles      = (v.M + BLOCK_M * cl - 1) / (BLOCK_M * cl);
+    gp.n_tiles      = (v.N + bn - 1) / bn;
+    gp.k_blocks     = (v.K + BLOCK_K - 1) / BLOCK_K;
+    gp.split_k      = split;
+    gp.kb_per_split = kb_per_split;
+    gp.group_m      = (uint32_t)cfg.raster;
+    const uint64_t work = (uint64_t)gp.batch * split * gp.m_tiles * gp.n_tiles;
+    if (work > 0x7fffffffull) return fail(B200_GEMM_ERR_BAD_SIZE, "too many tiles (%llu)", (unsigned long long)work);
+    gp.num_work      = (uint32_t)work;
+    const int umma_n = bn > 256 ? 256 : bn;
+    gp.a_mn_major    = v.a_mn ? 1u : 0u;
+    gp.b_mn_major    = v.b_mn ? 1u : 0u;
+    gp.idesc = (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | (gp.a_mn_major << 15) |
+               (gp.b_mn_major << 16) | ((uint32_t)(umma_n >> 3) << 17) | ((uint32_t)((BLOCK_M * cl) >> 4) << 24);
+    gp.stages = (uint32_t)cfg.stages;
+    gp.status = ctx->d_status;
+
+    float*      ws = ctx->d_ws; // device address resolved by cudaGetSymbolAddress, never the symbol itself
+    CUtensorMap tmA, tmB, tmD;
+    st = encode_operand(&tmA, bf16, v.a, v.M, v.K, p.batch, v.a_mn, BLOCK_M);
+    if (st == B200_GEMM_OK) st = encode_operand(&tmB, bf16, v.b, v.N, v.K, p.batch, v.b_mn, (uint32_t)umma_n / cl);
+    if (st == B200_GEMM_OK) {
+        if (split > 1)
+            st = encode_map(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ws, v.N, v.M, (uint64_t)p.batch * split, 32, 32);
+        else if (out == OUT_F32)
+            st = encode_map(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, v.d, v.N, v.M, p.batch, 32, 32);
+        else
+            st = encode_map(&tmD, out == OUT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                            v.d, v.N, v.M, p.batch, 64, 32);
+    }
+    if (st != B200_GEMM_OK) return st;
+
+    const uint32_t smem     = gemm_smem_bytes(bn, (int)cl, cfg.stages);
+    const uint32_t units    = std::min<uint32_t>(gp.num_work, (uint32_t)ctx->sm_count / cl);
+    const int      kern_out = split > 1 ? OUT_F32 : out;
+    cudaError_t    e;
+    if (cl == 2) {
+        if (bn == 128) e = launch_bn<128, 2>(kern_out, units, &ctx->pair_units[0], smem, stream, tmA, tmB, tmD, gp);
+        else if (bn == 256) e = launch_bn<256, 2>(kern_out, units, &ctx->pair_units[1], smem, stream, tmA, tmB, tmD, gp);
+        else e = launch_bn<512, 2>(kern_out, units, &ctx->pair_units[2], smem, stream, tmA, tmB, tmD, gp);
+    } else {
+        switch (bn) {
+            case 64: e = launch_bn<64, 1>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
+            case 128: e = launch_bn<128, 1>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
+            default: e = launch_bn<256, 1>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
+        }
+    }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (e != cudaSuccess) return fail(B200_GEMM_ERR_CUDA, "GEMM kernel launch failed: %s", cudaGetErrorString(e));
+
+    if (split > 1) {
+        const uint64_t mn     = (uint64_t)v.M * v.N;
+        const uint64_t total4 = mn * p.batch / 4;
+        const unsigned blocks = (unsigned)std::min<uint64_t>((total4 + 255) / 256, (uint64_t)ctx->sm_count * 8);
+        switch (out) {
+            case OUT_F32: splitk_reduce_kernel<OUT_F32><<<blocks, 256, 0, stream>>>(ws, v.d, mn, split, (uint32_t)p.batch); break;
+            case OUT_F16: splitk_reduce_kernel<OUT_F16><<<blocks, 256, 0, stream>>>(ws, v.d, mn, split, (uint32_t)p.batch); break;
+            default: splitk_reduce_kernel<OUT_BF16><<<blocks, 256, 0, stream>>>(ws, v.d, mn, split, (uint32_t)p.batch); break;
+        }
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return fail(B200_GEMM_ERR_CUDA, "split-K reduce launch failed: %s", cudaGetErrorString(e));
+    }
+    return B200_GEMM_OK;
+}
+
 } // namespace b200
 
 // ==============================================================================================
@@ -751,3 +924,19 @@ extern "C" int b200_gemm_last_status(void) { return t_last_status; }
 extern "C" const char* b200_gemm_last_error(void) { return t_last_error; }
 extern "C" const char* b200_gemm_version(void) { return "b200_gemm 0.1 (sm_100a)"; }
 extern "C" unsigned long long b200_gemm_launch_count(void) { return g_launches.load(); }
+
+extern "C" int b200_gemm_splitk_static(int types, void* C, const void* A, const void* B, size_t M, size_t N, size_t K,
+                                       size_t batch_count, int layout_c, int layout_a, int layout_b, void* stream,
+                                       const b200_gemm_config* cfg)
+{
+    t_last_status = B200_GEMM_OK;
+    try {
+        const Problem      p{types, C, A, B, M, N, K, batch_count, layout_c, layout_a, layout_b};
+        const cudaStream_t s = stream ? *static_cast<cudaStream_t*>(stream) : nullptr;
+        return run_gemm_static(p, s, cfg);
+    } catch (const std::exception& ex) {
+        return fail(B200_GEMM_ERR_CUDA, "exception: %s", ex.what());
+    } catch (...) {
+        return fail(B200_GEMM_ERR_CUDA, "unknown exception");
+    }
+}

@@ -44,7 +44,7 @@ SPACE = {
     "tile_m": [128, 256],
     "tile_n": [64, 128, 256, 512],
     "stages": [2, 3, 4, 5, 6, 8],
-    "split_k": [1, 2, 3, 4, 6, 8, 12, 16, 24, 32],
+    "split_k": [1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 12, 14, 16, 24, 32],
     "raster": [0, 1, 2, 4, 8, 16, 32],
 }
 SMEM_LIMIT = 232448          # bytes a CTA may use

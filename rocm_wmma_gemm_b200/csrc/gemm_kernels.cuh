@@ -47,12 +47,14 @@ struct GemmParams {
     uint32_t idesc;        // tcgen05 instruction descriptor
     uint32_t stages;       // ring depth actually used (<= MAX_STAGES)
     unsigned int* status;  // device status word
+    void*    out;          // transposed epilogue only: base of the (Nk x Mk, row-major) output
+    uint32_t k_skew;       // work unit w starts its K loop (w * k_skew) k-blocks in (0 = in order)
 };
 
 constexpr int      BLOCK_M        = 128;
 constexpr int      BLOCK_K        = 64; // 64 x 2 B = one 128-byte swizzle row
 constexpr int      UMMA_K         = 16;
-constexpr int      MAX_STAGES     = 8;
+constexpr int      MAX_STAGES     = 12;
 constexpr int      GEMM_THREADS   = 192; // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
 constexpr uint32_t A_TILE_BYTES   = BLOCK_M * BLOCK_K * 2;
 constexpr uint32_t EPI_BUF_BYTES  = 32 * 128; // one warp's 32 rows x 128 B
@@ -65,16 +67,17 @@ __host__ __device__ constexpr uint32_t stage_bytes(int bn, int cluster)
     return A_TILE_BYTES + static_cast<uint32_t>(bn / cluster) * BLOCK_K * 2;
 }
 
-// Dynamic shared memory a launch needs (1 KiB slack for manual 1024-byte alignment).
-__host__ __device__ constexpr uint32_t gemm_smem_bytes(int bn, int cluster, int stages)
+// Dynamic shared memory a launch needs (1 KiB slack for manual 1024-byte alignment).  The
+// transposed epilogue stores straight from registers and needs no staging.
+__host__ __device__ constexpr uint32_t gemm_smem_bytes(int bn, int cluster, int stages, bool transposed = false)
 {
-    return static_cast<uint32_t>(stages) * stage_bytes(bn, cluster) + EPI_BYTES + 1024;
+    return static_cast<uint32_t>(stages) * stage_bytes(bn, cluster) + (transposed ? 0u : EPI_BYTES) + 1024;
 }
 
 // Deepest ring that fits the 227 KiB a CTA may use (static barriers included).
-__host__ __device__ constexpr int max_stages(int bn, int cluster)
+__host__ __device__ constexpr int max_stages(int bn, int cluster, bool transposed = false)
 {
-    int s = static_cast<int>((232448u - 512u - EPI_BYTES - 1024u) / stage_bytes(bn, cluster));
+    int s = static_cast<int>((232448u - 512u - (transposed ? 0u : EPI_BYTES) - 1024u) / stage_bytes(bn, cluster));
     return s > MAX_STAGES ? MAX_STAGES : s;
 }
 
@@ -205,14 +208,16 @@ __device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits)
 // Edges: TMA zero-fills out-of-range loads (M, N and K tails) and clips stores.
 // No TMA load here uses cluster multicast.
 // ---------------------------------------------------------------------------------------------
-template <int BN, int OUT, int CL>
+template <int BN, int OUT, int CL, bool TR = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA,
                      const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ CUtensorMap tmD, const GemmParams p)
 {
-    static_assert(BN == 64 || BN == 128 || BN == 256 || BN == 512, "BN must be 64, 128, 256 or 512");
+    static_assert(BN == 16 || BN == 32 || BN == 64 || BN == 128 || BN == 256 || BN == 512,
+                  "BN must be 16, 32, 64, 128, 256 or 512");
     static_assert(CL == 1 || CL == 2, "cluster size must be 1 or 2");
+    static_assert(!TR || CL == 1, "the transposed epilogue is a one-CTA variant");
     // One MMA covers at most 256 columns: a 512-wide tile is two sub-tiles that share the A'
     // operand of every K slice (A' is staged once for 512 columns of output).
     constexpr int      UMMA_N       = BN > 256 ? 256 : BN;
@@ -225,11 +230,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     // TMEM holds 512 f32 columns: two accumulators (epilogue of tile i overlaps the main loop
     // of tile i + 1) up to BN = 256, a single one for BN = 512.
     constexpr uint32_t NUM_ACC      = BN > 256 ? 1 : 2;
-    constexpr uint32_t TMEM_COLS    = NUM_ACC * BN; // power of two >= 32
+    constexpr uint32_t ACC_COLS     = BN < 64 ? 64 : BN; // the epilogue reads up to 64 columns at a time
+    constexpr uint32_t TMEM_COLS    = NUM_ACC * ACC_COLS; // power of two >= 32
     constexpr int      OUT_BYTES    = (OUT == OUT_F32) ? 4 : 2;
     constexpr int      CH           = 128 / OUT_BYTES; // output columns per 128-byte chunk
-    constexpr int      NCHUNK       = BN / CH;
-    static_assert(SUB_ROWS >= 64, "each CTA stages at least 64 rows of B' per sub-tile");
+    constexpr int      NCHUNK       = BN < CH ? 1 : BN / CH; // a narrow tile is one (clipped) chunk
+    static_assert(SUB_ROWS >= 16, "each CTA stages at least 16 rows of B' per sub-tile");
+    // (an MN-major B' is loaded in 64-row boxes: the host only picks BN >= 64 * CL for it)
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t s_full[MAX_STAGES];
@@ -249,7 +256,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     const uint32_t units  = gridDim.x / CL;
 
     const uint32_t ring = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u; // ring of operand tiles
-    const uint32_t epi  = ring + stages * STAGE_BYTES;                // epilogue staging
+    const uint32_t epi  = ring + stages * STAGE_BYTES;                // epilogue staging (unused when TR)
 
     if (tid == 0) {
         ptx::prefetch_tensormap(&tmA);
@@ -288,7 +295,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 const WorkCoord c  = decode_work(p, w, BN, BLOCK_M * CL);
                 const int32_t   am = static_cast<int32_t>(c.m0 + rank * BLOCK_M);
                 const int32_t   bn = static_cast<int32_t>(c.n0 + rank * SUB_ROWS);
-                for (uint32_t kb = c.kb0; kb < c.kb1; ++kb) {
+                // Streaming (HBM-bound) problems rotate each work unit's K order so that the CTAs
+                // running at the same time read different K offsets: rows of a K-major operand
+                // are a power of two apart, and same-offset reads from thousands of rows land on
+                // a few memory channels.
+                const uint32_t nkb = c.kb1 - c.kb0;
+                const uint32_t rot = p.k_skew ? static_cast<uint32_t>((static_cast<uint64_t>(w) * p.k_skew) % nkb) : 0u;
+                for (uint32_t i = 0; i < nkb; ++i) {
+                    const uint32_t kb = c.kb0 + (i + rot >= nkb ? i + rot - nkb : i + rot);
                     ok = bounded_wait(ptx::smem_u32(&s_empty[stage]), phase ^ 1u, &s_abort,
                                       p.status, ST_PRODUCER_WAIT);
                     if (!ok) break;
@@ -369,7 +383,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                                            p.status, ST_MMA_WAIT_ACC);
                 if (!ok) break;
                 ptx::tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * BN;
+                const uint32_t d_tmem = tmem_base + buf * ACC_COLS;
                 for (uint32_t kb = c.kb0; kb < c.kb1; ++kb) {
                     ok = bounded_wait(ptx::smem_u32(&s_full[stage]), phase, &s_abort, p.status,
                                       ST_MMA_WAIT_FULL);
@@ -426,9 +440,44 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             ptx::tc_fence_after();
             const uint32_t row0     = c.m0 + rank * BLOCK_M + q * 32u;
             const bool     row_live = row0 < p.M;
+            const uint32_t tacc = tmem_base + ((q * 32u) << 16) + buf * ACC_COLS;
+            if constexpr (TR) {
+                // Transposed epilogue: D(i, j) goes to out[j * M + i].  Each lane owns row i, so
+                // for a fixed column j the warp writes 32 consecutive elements: coalesced stores
+                // straight from registers, no staging.  Used when the caller's small dimension
+                // had to become the MMA's N extent (skinny problems).
+                const uint32_t i = c.m0 + q * 32u + lane;
+#pragma unroll 1
+                for (int ch = 0; ch < (BN + 31) / 32; ++ch) {
+                    uint32_t v[32];
+                    ptx::tmem_ld_32x32(tacc + ch * 32, v);
+                    ptx::tmem_ld_wait(v);
+                    if (ch == (BN + 31) / 32 - 1) {
+                        ptx::tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&s_tempty[buf]));
+                    }
+                    if (i < p.M) {
+                        const size_t base = (static_cast<size_t>(c.z_out) * p.N + c.n0 + ch * 32) * p.M + i;
+#pragma unroll
+                        for (int r = 0; r < 32; ++r) {
+                            if (ch * 32 + r < BN && c.n0 + ch * 32 + r < p.N) {
+                                const size_t at = base + static_cast<size_t>(r) * p.M;
+                                if constexpr (OUT == OUT_F32) {
+                                    static_cast<float*>(p.out)[at] = __uint_as_float(v[r]);
+                                } else if constexpr (OUT == OUT_F16) {
+                                    static_cast<__half*>(p.out)[at] = __float2half_rn(__uint_as_float(v[r]));
+                                } else {
+                                    static_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(__uint_as_float(v[r]));
+                                }
+                            }
+                        }
+                    }
+                }
+                continue;
+            }
             // Software pipeline over 128-byte column chunks: the TMEM load of chunk ch + 1 is
             // in flight while chunk ch is converted, staged and handed to the TMA store.
-            const uint32_t tacc = tmem_base + ((q * 32u) << 16) + buf * BN;
             uint32_t       n0[32], n1[32]; // raw accumulator words of the chunk in flight
             ptx::tmem_ld_32x32(tacc, n0);
             if constexpr (OUT != OUT_F32) ptx::tmem_ld_32x32(tacc + 32u, n1);

@@ -17,6 +17,7 @@
 #include <cstring>
 #include <limits>
 #include <mutex>
+#include <vector>
 
 namespace b200 {
 
@@ -153,6 +154,14 @@ struct DeviceCtx {
     int           sm_count = 0;
     int           pair_units[3] = {0, 0, 0}; // co-resident CTA pairs for tile_n 128 / 256 / 512 (0 = not asked yet)
     unsigned int* d_status = nullptr;
+    // split-K workspaces, one per stream that has used split-K (calls on one stream are ordered,
+    // so they can share a buffer; calls on different streams must not)
+    struct Workspace {
+        cudaStream_t stream;
+        float*       ptr;
+        size_t       bytes;
+    };
+    std::vector<Workspace> workspaces;
     // host-buffer path
     cudaStream_t h_stream = nullptr;
     void*        h_buf[3] = {nullptr, nullptr, nullptr};
@@ -182,6 +191,27 @@ static cudaError_t set_smem_attr()
     cudaError_t e = set_smem_attr_one<BN, OUT_F32, CL>();
     if (e == cudaSuccess) e = set_smem_attr_one<BN, OUT_F16, CL>();
     if (e == cudaSuccess) e = set_smem_attr_one<BN, OUT_BF16, CL>();
+    return e;
+}
+
+// Narrow one-CTA variants (BN <= 128) with the staged or the transposed epilogue.
+template <int BN, int OUT>
+static cudaError_t set_smem_attr_narrow_one()
+{
+    cudaError_t e = cudaFuncSetAttribute(gemm_umma_kernel<BN, OUT, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)gemm_smem_bytes(BN, 1, max_stages(BN, 1, true), true));
+    if (e == cudaSuccess && BN < 64)
+        e = cudaFuncSetAttribute(gemm_umma_kernel<BN, OUT, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)gemm_smem_bytes(BN, 1, max_stages(BN, 1, false), false));
+    return e;
+}
+
+template <int BN>
+static cudaError_t set_smem_attr_narrow()
+{
+    cudaError_t e = set_smem_attr_narrow_one<BN, OUT_F32>();
+    if (e == cudaSuccess) e = set_smem_attr_narrow_one<BN, OUT_F16>();
+    if (e == cudaSuccess) e = set_smem_attr_narrow_one<BN, OUT_BF16>();
     return e;
 }
 
@@ -219,9 +249,41 @@ static int get_ctx(DeviceCtx** out)
         CUDA_TRY((set_smem_attr<128, 2>()));
         CUDA_TRY((set_smem_attr<256, 2>()));
         CUDA_TRY((set_smem_attr<512, 2>()));
+        CUDA_TRY((set_smem_attr_narrow<16>()));
+        CUDA_TRY((set_smem_attr_narrow<32>()));
+        CUDA_TRY((set_smem_attr_narrow<64>()));
+        CUDA_TRY((set_smem_attr_narrow<128>()));
         c.ready = true;
     }
     *out = &c;
+    return B200_GEMM_OK;
+}
+
+// Split-K workspace of at least `bytes` for `stream`: cached per stream and grown on demand, so
+// the steady state allocates nothing (an allocation per call costs more than a skinny GEMM).
+static int get_workspace(DeviceCtx* ctx, cudaStream_t stream, size_t bytes, float** out)
+{
+    std::lock_guard<std::mutex> lock(g_mutex);
+    for (auto& w : ctx->workspaces) {
+        if (w.stream != stream) continue;
+        if (w.bytes < bytes) {
+            // The old buffer may still be in use by work queued on this stream.
+            CUDA_TRY(cudaStreamSynchronize(stream));
+            CUDA_TRY(cudaFree(w.ptr));
+            w.ptr   = nullptr;
+            w.bytes = 0;
+            const size_t want = bytes + bytes / 4;
+            CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&w.ptr), want));
+            w.bytes = want;
+        }
+        *out = w.ptr;
+        return B200_GEMM_OK;
+    }
+    DeviceCtx::Workspace w{stream, nullptr, 0};
+    CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&w.ptr), bytes));
+    w.bytes = bytes;
+    ctx->workspaces.push_back(w);
+    *out = w.ptr;
     return B200_GEMM_OK;
 }
 
@@ -294,6 +356,18 @@ static int validate(const Problem& p)
         (reinterpret_cast<uintptr_t>(p.B) % 2))
         return fail(B200_GEMM_ERR_MISALIGNED, "a pointer is not aligned to its element size");
     return B200_GEMM_OK;
+}
+
+// Can TMA address the two operands of this view (bases 16-byte aligned, contiguous extents
+// multiples of 8 elements)?
+static bool operands_tma_ok(const Problem& p, const View& v)
+{
+    if (reinterpret_cast<uintptr_t>(v.a) % 16 || reinterpret_cast<uintptr_t>(v.b) % 16) return false;
+    const uint32_t a_inner = v.a_mn ? v.M : v.K;
+    const uint32_t b_inner = v.b_mn ? v.N : v.K;
+    if (a_inner % 8 || b_inner % 8) return false;
+    if (p.batch > 1 && (((size_t)v.M * v.K) % 8 || ((size_t)v.N * v.K) % 8)) return false;
+    return true;
 }
 
 // Can TMA address this view?  Needs 16-byte aligned bases and 16-byte multiples for every
@@ -408,7 +482,7 @@ static int encode_operand(CUtensorMap* tm, bool bf16, const void* base, uint32_t
 // ------------------------------------------------------------------------------------------
 // Launch
 // ------------------------------------------------------------------------------------------
-template <int BN, int CL>
+template <int BN, int CL, bool TR = false>
 static cudaError_t launch_bn(int out, uint32_t units_wanted, int* pair_units, uint32_t smem, cudaStream_t s,
                              const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& d,
                              const GemmParams& gp)
@@ -430,7 +504,7 @@ static cudaError_t launch_bn(int out, uint32_t units_wanted, int* pair_units, ui
             q.attrs                = qa;
             q.numAttrs             = 1;
             int         n  = 0;
-            cudaError_t qe = cudaOccupancyMaxActiveClusters(&n, gemm_umma_kernel<BN, OUT_F32, CL>, &q);
+            cudaError_t qe = cudaOccupancyMaxActiveClusters(&n, gemm_umma_kernel<BN, OUT_F32, CL, TR>, &q);
             if (qe != cudaSuccess || n < 1) {
                 (void)cudaGetLastError();
                 n = 64;
@@ -451,9 +525,9 @@ static cudaError_t launch_bn(int out, uint32_t units_wanted, int* pair_units, ui
     lc.attrs                 = attr;
     lc.numAttrs              = 1;
     switch (out) {
-        case OUT_F32: return cudaLaunchKernelEx(&lc, gemm_umma_kernel<BN, OUT_F32, CL>, a, b, d, gp);
-        case OUT_F16: return cudaLaunchKernelEx(&lc, gemm_umma_kernel<BN, OUT_F16, CL>, a, b, d, gp);
-        default: return cudaLaunchKernelEx(&lc, gemm_umma_kernel<BN, OUT_BF16, CL>, a, b, d, gp);
+        case OUT_F32: return cudaLaunchKernelEx(&lc, gemm_umma_kernel<BN, OUT_F32, CL, TR>, a, b, d, gp);
+        case OUT_F16: return cudaLaunchKernelEx(&lc, gemm_umma_kernel<BN, OUT_F16, CL, TR>, a, b, d, gp);
+        default: return cudaLaunchKernelEx(&lc, gemm_umma_kernel<BN, OUT_BF16, CL, TR>, a, b, d, gp);
     }
 }
 
@@ -493,8 +567,20 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
         return B200_GEMM_OK;
     }
 
-    const View v = make_view(p);
-    if (!tma_ok(p, v)) {
+    View v = make_view(p);
+    // Skinny problems: the MMA's M extent is fixed at 128 rows but its N extent goes down to 16,
+    // so when the kernel view has few rows and many columns the operands swap roles once more
+    // (the kernel computes D^T) and the epilogue writes D^T transposed, i.e. D.  No 128-row
+    // tile of mostly zero-filled A' is staged and the ring holds twice as many slots.
+    bool transposed = false;
+    if (v.M <= 64 && v.N >= 128 && operands_tma_ok(p, v) && reinterpret_cast<uintptr_t>(v.d) % 16 == 0 &&
+        ((size_t)v.M * v.N) % 4 == 0) {
+        std::swap(v.a, v.b);
+        std::swap(v.M, v.N);
+        std::swap(v.a_mn, v.b_mn);
+        transposed = true;
+    }
+    if (!transposed && !tma_ok(p, v)) {
         cudaError_t e;
         switch (p.types) {
             case B200_GEMM_F16_F16: e = launch_generic<__half, __half>(p, stream); break;
@@ -509,9 +595,25 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     b200_gemm_config cfg = resolve_config(p, user_cfg, nullptr);
     st                   = check_config(cfg);
     if (st != B200_GEMM_OK) return st;
+    // Narrow kernel views (at most 64 columns) run on the narrow one-CTA variants whatever
+    // tile the table names: tile_n is the smallest compiled width that covers N (an MN-major
+    // B' is loaded in 64-row boxes, so it needs 64) and the ring is as deep as fits.
+    const bool narrow = v.N <= 64 || transposed;
+    if (narrow) {
+        cfg.tile_m  = BLOCK_M;
+        cfg.cluster = 1;
+        cfg.tile_n  = v.N <= 16 ? 16 : (v.N <= 32 ? 32 : (v.N <= 64 ? 64 : 128));
+        if (v.b_mn && cfg.tile_n < 64) cfg.tile_n = 64;
+        cfg.stages = max_stages(cfg.tile_n, 1, transposed);
+    }
     uint32_t kb_per_split = 0;
     legalize(cfg, v, &kb_per_split);
+    if (narrow) cfg.stages = max_stages(cfg.tile_n, 1, transposed);
 
+    if (!user_cfg && cfg.split_k > 1 && !transposed && v.N % 4) { // the table's nearest entry may not fit
+        cfg.split_k = 1;
+        legalize(cfg, v, &kb_per_split);
+    }
     const int      bn   = cfg.tile_n;
     const int      out  = out_kind(p.types);
     const bool     bf16 = in_is_bf16(p.types);
@@ -542,19 +644,27 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
                (gp.b_mn_major << 16) | ((uint32_t)(umma_n >> 3) << 17) | ((uint32_t)((BLOCK_M * cl) >> 4) << 24);
     gp.stages = (uint32_t)cfg.stages;
     gp.status = ctx->d_status;
+    gp.out    = nullptr;
+    // Streaming (HBM-bound) views rotate the K order per work unit; see the producer.
+    const bool streaming = narrow || std::min(v.M, v.N) <= 256;
+    gp.k_skew = streaming ? std::max<uint32_t>(1u, kb_per_split / std::max<uint32_t>(1u, std::min<uint32_t>((uint32_t)work, (uint32_t)ctx->sm_count))) : 0u;
 
-    // Split-K partials go to a stream-ordered f32 workspace laid out [batch][split][Mk][Nk].
+    // Split-K partials go to this stream's cached f32 workspace, laid out [batch][split][Mk][Nk].
     float*       ws       = nullptr;
     const size_t ws_bytes = split > 1 ? (size_t)p.batch * split * v.M * v.N * sizeof(float) : 0;
     if (split > 1) {
-        if (v.N % 4) return fail(B200_GEMM_ERR_BAD_CONFIG, "split_k needs N %% 4 == 0 in the kernel view");
-        CUDA_TRY(cudaMallocAsync(reinterpret_cast<void**>(&ws), ws_bytes, stream));
+        if (!transposed && v.N % 4) return fail(B200_GEMM_ERR_BAD_CONFIG, "split_k needs N %% 4 == 0 in the kernel view");
+        st = get_workspace(ctx, stream, ws_bytes, &ws);
+        if (st != B200_GEMM_OK) return st;
     }
 
     CUtensorMap tmA, tmB, tmD;
     st = encode_operand(&tmA, bf16, v.a, v.M, v.K, p.batch, v.a_mn, BLOCK_M);
     if (st == B200_GEMM_OK) st = encode_operand(&tmB, bf16, v.b, v.N, v.K, p.batch, v.b_mn, (uint32_t)umma_n / cl);
-    if (st == B200_GEMM_OK) {
+    if (st == B200_GEMM_OK && transposed) {
+        tmD    = tmA; // not used by the transposed epilogue; any valid descriptor will do
+        gp.out = split > 1 ? static_cast<void*>(ws) : v.d;
+    } else if (st == B200_GEMM_OK) {
         if (split > 1)
             st = encode_map(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ws, v.N, v.M, (uint64_t)p.batch * split, 32, 32);
         else if (out == OUT_F32)
@@ -563,21 +673,27 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
             st = encode_map(&tmD, out == OUT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                             v.d, v.N, v.M, p.batch, 64, 32);
     }
-    if (st != B200_GEMM_OK) {
-        if (ws) cudaFreeAsync(ws, stream);
-        return st;
-    }
+    if (st != B200_GEMM_OK) return st;
 
-    const uint32_t smem     = gemm_smem_bytes(bn, (int)cl, cfg.stages);
+    const uint32_t smem     = gemm_smem_bytes(bn, (int)cl, cfg.stages, transposed);
     const uint32_t units    = std::min<uint32_t>(gp.num_work, (uint32_t)ctx->sm_count / cl);
     const int      kern_out = split > 1 ? OUT_F32 : out;
     cudaError_t    e;
-    if (cl == 2) {
+    if (transposed) {
+        switch (bn) {
+            case 16: e = launch_bn<16, 1, true>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
+            case 32: e = launch_bn<32, 1, true>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
+            case 64: e = launch_bn<64, 1, true>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
+            default: e = launch_bn<128, 1, true>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
+        }
+    } else if (cl == 2) {
         if (bn == 128) e = launch_bn<128, 2>(kern_out, units, &ctx->pair_units[0], smem, stream, tmA, tmB, tmD, gp);
         else if (bn == 256) e = launch_bn<256, 2>(kern_out, units, &ctx->pair_units[1], smem, stream, tmA, tmB, tmD, gp);
         else e = launch_bn<512, 2>(kern_out, units, &ctx->pair_units[2], smem, stream, tmA, tmB, tmD, gp);
     } else {
         switch (bn) {
+            case 16: e = launch_bn<16, 1>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
+            case 32: e = launch_bn<32, 1>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
             case 64: e = launch_bn<64, 1>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
             case 128: e = launch_bn<128, 1>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
             default: e = launch_bn<256, 1>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
@@ -585,7 +701,6 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     }
     g_launches.fetch_add(1, std::memory_order_relaxed);
     if (e != cudaSuccess) {
-        if (ws) cudaFreeAsync(ws, stream);
         return fail(B200_GEMM_ERR_CUDA, "GEMM kernel launch failed: %s (tile_n=%d stages=%d smem=%u)", cudaGetErrorString(e), bn,
                     cfg.stages, smem);
     }
@@ -601,7 +716,6 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
         }
         g_launches.fetch_add(1, std::memory_order_relaxed);
         e = cudaGetLastError();
-        cudaFreeAsync(ws, stream);
         if (e != cudaSuccess) return fail(B200_GEMM_ERR_CUDA, "split-K reduce launch failed: %s", cudaGetErrorString(e));
     }
     return B200_GEMM_OK;
@@ -745,6 +859,8 @@ static int run_gemm_static(const Problem& p, cudaStream_t stream, const b200_gem
                (gp.b_mn_major << 16) | ((uint32_t)(umma_n >> 3) << 17) | ((uint32_t)((BLOCK_M * cl) >> 4) << 24);
     gp.stages = (uint32_t)cfg.stages;
     gp.status = ctx->d_status;
+    gp.out    = nullptr;
+    gp.k_skew = 0;
 
     float*      ws = ctx->d_ws; // device address resolved by cudaGetSymbolAddress, never the symbol itself
     CUtensorMap tmA, tmB, tmD;

@@ -259,3 +259,38 @@ def test_tuned_table_configs_run():
 def test_device_status_is_clean():
     assert g.device_status() == 0
     assert g.launch_count() > 0
+
+
+SKINNY = [(16, 1024, 512), (8, 256, 2048), (24, 136, 264), (40, 2048, 128), (64, 512, 576), (1, 128, 64), (48, 4096, 1024),
+          (1024, 16, 512), (2048, 8, 256), (512, 24, 264), (640, 40, 128), (4096, 64, 192), (256, 32, 1024)]
+
+
+@pytest.mark.parametrize("M,N,K", SKINNY)
+def test_skinny_shapes(M, N, K):
+    """One small dimension (<= 64): the narrow tile variants (16 / 32 / 64 columns) and, when the
+    small dimension is the kernel's row extent, the operand swap with the transposing epilogue.
+    All 8 layouts and 4 type pairs; split-K on top for the deep ones."""
+    for types in range(4):
+        bf16 = types >= 2
+        for (la, lb, lc) in LAYOUTS:
+            A, B = seeded(M, N, K, la, lb, bf16)
+            ref = oracle.hgemm(types, A, B, M, N, K, lc, la, lb)
+            got = gpu_gemm(types, A, B, M, N, K, lc, la, lb)
+            check_parity(types, got, ref, K, SIGMA_UNIFORM, M, N, lc)
+            if K >= 512:
+                cfg = g.GemmConfig(128, 128, 4, 1, 3, 0)
+                got = gpu_gemm(types, A, B, M, N, K, lc, la, lb, config=cfg)
+                check_parity(types, got, ref, K, SIGMA_UNIFORM, M, N, lc)
+
+
+def test_skinny_batched():
+    M, N, K, batch = 16, 512, 256, 3
+    for types in (1, 2):
+        bf16 = types >= 2
+        for (la, lb, lc) in [(0, 1, 0), (0, 0, 0), (1, 0, 1)]:
+            A = np.concatenate([oracle.init_matrix(M, K, la, bf16)[(np.arange(M * K) + 13 * b) % (M * K)] for b in range(batch)])
+            B = np.concatenate([oracle.init_matrix(K, N, lb, bf16)[(np.arange(K * N) + 7 * b) % (K * N)] for b in range(batch)])
+            got = gpu_gemm(types, A, B, M, N, K, lc, la, lb, batch=batch)
+            for b in range(batch):
+                ref = oracle.hgemm(types, A[b * M * K:(b + 1) * M * K], B[b * K * N:(b + 1) * K * N], M, N, K, lc, la, lb)
+                check_parity(types, got[b * M * N:(b + 1) * M * N], ref, K, SIGMA_UNIFORM, M, N, lc)

@@ -1,0 +1,156 @@
+#!/usr/bin/env python
+"""Per-shape x layout benchmark of the GEMM library.
+
+Counterpart of the reference's benchmark binaries (benchmark/gemm/bench_{half_half,float_half,
+bf16_bf16,float_bf16}.cpp of adelj88/rocm_wmma_gemm): for every requested shape and each of the
+eight row/column-major combinations of A, B and C it times the GEMM with device events and
+reports TFLOP/s (2*M*N*K*batch / t, the reference's count), GB/s of algorithmic bytes, the
+fraction of the tensor and HBM rooflines, and the configuration the tuned table chose.
+Benchmark names use the reference's format `{A:m_layout::row_major,B:...,C:...,m:..,n:..,k:..}`.
+
+    python -m rocm_wmma_gemm_b200.bench_shapes --type f16_f16 --shapes 1024,1024,1024 8192,8192,8192
+    python -m rocm_wmma_gemm_b200.bench_shapes --preset skinny --json out.jsonl
+
+Presets are the target configurations: `squares` (fp16->fp16, 1024..8192 cubed, uniform[-1,1]),
+`projections` (bf16->f32 transformer shapes, normal(0, 0.02), A row / B col / C row),
+`skinny` (fp16->f32, M in {16, 64, 128}, uniform[-1,1], B row and col), `large` (bf16->bf16
+16384^3 and 32768x32768x8192, normal(0, 1)).  `--fill cyclic` uses the reference benchmarks'
+five-value pattern (benchmark/bench.hpp:37-52) instead of random values.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import sys
+
+import torch
+
+import rocm_wmma_gemm_b200 as g
+
+LAYOUT = {0: "m_layout::row_major", 1: "m_layout::col_major"}
+TYPES = {"f16_f16": 0, "f32_f16": 1, "bf16_bf16": 2, "f32_bf16": 3}
+ALL_LAYOUTS = [(la, lb, lc) for la in (0, 1) for lb in (0, 1) for lc in (0, 1)]
+NOMINAL_TFLOPS, NOMINAL_GBS = 2250.0, 8000.0
+
+PRESETS = {
+    "squares": dict(type="f16_f16", fill="uniform", shapes=[(n, n, n) for n in (1024, 2048, 4096, 8192)], layouts=ALL_LAYOUTS),
+    "projections": dict(type="f32_bf16", fill="normal0.02", layouts=[(0, 1, 0)],
+                        shapes=[(4096, 4096, 2048), (4096, 5120, 5120), (8192, 28672, 8192), (8192, 8192, 28672)]),
+    "skinny": dict(type="f32_f16", fill="uniform", layouts=[(0, 0, 0), (0, 1, 0)],
+                   shapes=[(m, n, 8192) for n in (8192, 28672) for m in (16, 64, 128)]),
+    "large": dict(type="bf16_bf16", fill="normal1", layouts=[(0, 1, 0)], shapes=[(16384, 16384, 16384), (32768, 32768, 8192)]),
+    "headline": dict(type="f32_bf16", fill="normal0.02", layouts=ALL_LAYOUTS, shapes=[(8192, 8192, 8192)]),
+}
+
+
+def make(n, dtype, fill, gen):
+    if fill == "cyclic":
+        vals = torch.tensor([0.1, 0.125, 0.15, 0.175, 0.2], device="cuda")
+        return vals[torch.arange(n, device="cuda") % 5].to(dtype)
+    if fill == "uniform":
+        return (torch.rand(n, device="cuda", generator=gen) * 2 - 1).to(dtype)
+    sigma = float(fill.replace("normal", "") or 1.0)
+    return (torch.randn(n, device="cuda", generator=gen) * sigma).to(dtype)
+
+
+def load_peaks():
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f)
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def bench_one(L, types, M, N, K, la, lb, lc, batch, fill, warmup, iters, gen):
+    in_dt = torch.bfloat16 if types >= 2 else torch.float16
+    out_dt = torch.float32 if types in (1, 3) else in_dt
+    A = make(M * K * batch, in_dt, fill, gen)
+    B = make(K * N * batch, in_dt, fill, gen)
+    C = torch.empty(M * N * batch, device="cuda", dtype=out_dt)
+    for _ in range(warmup):
+        L.gemm(C, A, B, M, N, K, lc, la, lb, batch_count=batch)
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for e0, e1 in ev:  # each call timed on its own, as the reference does
+        e0.record()
+        L.gemm(C, A, B, M, N, K, lc, la, lb, batch_count=batch)
+        e1.record()
+    torch.cuda.synchronize()
+    g.device_status()
+    ms = sorted(e0.elapsed_time(e1) for e0, e1 in ev)
+    # sustained: back to back, one pair of events
+    e0, e1 = ev[0]
+    e0.record()
+    for _ in range(iters):
+        L.gemm(C, A, B, M, N, K, lc, la, lb, batch_count=batch)
+    e1.record()
+    torch.cuda.synchronize()
+    back_to_back = e0.elapsed_time(e1) / iters
+    return ms, back_to_back, A.element_size(), C.element_size()
+
+
+def main(argv=None):
+    p = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    p.add_argument("--preset", choices=list(PRESETS))
+    p.add_argument("--type", choices=list(TYPES))
+    p.add_argument("--shapes", nargs="*", help="M,N,K ...")
+    p.add_argument("--layouts", nargs="*", help="A,B,C letters, e.g. r,c,r (default: all 8)")
+    p.add_argument("--batch_count", type=int, default=1)
+    p.add_argument("--fill", default=None, help="cyclic | uniform | normal<sigma>")
+    p.add_argument("--warmup", type=int, default=10)
+    p.add_argument("--iters", type=int, default=50)
+    p.add_argument("--json", help="append one JSON record per benchmark to this file")
+    a = p.parse_args(argv)
+
+    spec = dict(PRESETS[a.preset]) if a.preset else dict(type="f16_f16", fill="cyclic", layouts=ALL_LAYOUTS,
+                                                         shapes=[(n, n, n) for n in (1024, 2048, 4096, 8192)])
+    if a.type:
+        spec["type"] = a.type
+    if a.fill:
+        spec["fill"] = a.fill
+    if a.shapes:
+        spec["shapes"] = [tuple(int(x) for x in s.split(",")) for s in a.shapes]
+    if a.layouts:
+        spec["layouts"] = [tuple({"r": 0, "c": 1}[x] for x in t.split(",")) for t in a.layouts]
+
+    types = TYPES[spec["type"]]
+    peaks = load_peaks()
+    L = g.loader()
+    gen = torch.Generator(device="cuda").manual_seed(2024)
+    out = open(a.json, "a") if a.json else None
+    print(f"# {torch.cuda.get_device_name(0)}  type={spec['type']} fill={spec['fill']} batch={a.batch_count} "
+          f"(peaks: {peaks.get('bf16_tflops')} TFLOP/s burst, {peaks.get('hbm_gbs')} GB/s measured; nominal 2250 / 8000)")
+    print(f"{'benchmark':86s} {'min ms':>9s} {'med ms':>9s} {'TFLOP/s':>8s} {'sustained':>9s} {'GB/s':>7s} {'%tensor':>7s} {'%hbm':>6s}  config")
+    for (M, N, K) in spec["shapes"]:
+        for (la, lb, lc) in spec["layouts"]:
+            ms, b2b, in_sz, out_sz = bench_one(L, types, M, N, K, la, lb, lc, a.batch_count, spec["fill"], a.warmup, a.iters, gen)
+            flops = 2.0 * M * N * K * a.batch_count
+            nbytes = (in_sz * (M * K + K * N) + out_sz * M * N) * a.batch_count
+            med = statistics.median(ms)
+            cfg, idx = g.get_gemm_params(M, N, K, lc, la, lb, 1 if types in (1, 3) else 0)
+            name = f"{{A:{LAYOUT[la]},B:{LAYOUT[lb]},C:{LAYOUT[lc]},m:{M},n:{N},k:{K}}}"
+            rec = {"name": name, "type": spec["type"], "fill": spec["fill"], "batch": a.batch_count, "M": M, "N": N, "K": K,
+                   "layout": {"A": la, "B": lb, "C": lc}, "min_time_ms": ms[0], "median_time_ms": med, "max_time_ms": ms[-1],
+                   "avg_tflops": statistics.mean(flops / (t * 1e-3) / 1e12 for t in ms),
+                   "tflops_median": flops / (med * 1e-3) / 1e12, "tflops_sustained": flops / (b2b * 1e-3) / 1e12,
+                   "gbs_median": nbytes / (med * 1e-3) / 1e9, "algorithmic_bytes": nbytes,
+                   "pct_of_nominal_tensor": 100 * flops / (med * 1e-3) / 1e12 / NOMINAL_TFLOPS,
+                   "pct_of_measured_tensor": 100 * flops / (med * 1e-3) / 1e12 / peaks["bf16_tflops"],
+                   "pct_of_nominal_hbm": 100 * nbytes / (med * 1e-3) / 1e9 / NOMINAL_GBS,
+                   "pct_of_measured_hbm": 100 * nbytes / (med * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                   "config": cfg.as_dict(), "config_index": idx}
+            print(f"{name:86s} {ms[0]:9.4f} {med:9.4f} {rec['tflops_median']:8.1f} {rec['tflops_sustained']:9.1f} "
+                  f"{rec['gbs_median']:7.0f} {rec['pct_of_nominal_tensor']:7.1f} {rec['pct_of_nominal_hbm']:6.1f}  "
+                  f"{cfg.tile_m}x{cfg.tile_n} s{cfg.stages} k{cfg.split_k} r{cfg.raster}", flush=True)
+            if out:
+                out.write(json.dumps(rec) + "\n")
+                out.flush()
+    if out:
+        out.close()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -83,7 +83,8 @@ def test_every_table_config_is_a_compiled_variant():
 
 
 def test_generator_is_deterministic_and_sorted(tmp_path):
-    configs, rows, default_idx = generate_config.build_table(os.path.join(CFG_DIR, "gemm_config_sm100_f16.json"))
+    configs, rows, default_idx = generate_config.build_table(os.path.join(CFG_DIR, "gemm_config_sm100_f16.json"),
+                                                             os.path.join(CFG_DIR, "gemm_config_sm100_f32.json"))
     assert configs == sorted(set(configs)) and configs[default_idx] == generate_config.DEFAULT_CONFIG
     assert [r[0] for r in rows] == sorted(r[0] for r in rows)
     text = generate_config.render(configs, rows, default_idx, ["x.json"])

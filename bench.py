@@ -38,8 +38,8 @@ LAYOUTS = [(la, lb, lc) for la in (0, 1) for lb in (0, 1) for lc in (0, 1)]  # (
 LAYOUT_NAMES = ["".join("rc"[x] for x in l) for l in LAYOUTS]
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # DRAM bytes (read + write) of one 8192^3 bf16->f32 launch of gemm_umma_kernel, from the ncu
-# capture summarised in profiles/; None until measured.
-NCU_DRAM_BYTES_PER_LAUNCH_8192 = None
+# capture summarised in profiles/.
+NCU_DRAM_BYTES_PER_LAUNCH_8192 = 1.360e9  # 1.123 GB read + 0.237 GB write (profiles/gemm_umma_256x512_8192cubed_bf16_f32.md)
 
 
 def load_peaks():

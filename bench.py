@@ -152,10 +152,13 @@ def cpu_rows_runner(types, M, N, K, lc, la, lb, A, B):
 
 
 def calibrate_rows(run, M, cores, target_s):
-    rows = min(M, cores)
-    t = run(rows)
-    per_row = t / rows
-    want = int(max(cores, min(M, target_s / max(per_row, 1e-9))))
+    """Rows of C that take about target_s: two short runs separate the fixed cost of a call
+    (placing B in the reference's matrix class) from the cost per row."""
+    r1, r2 = min(M, cores), min(M, 4 * cores)
+    t1, t2 = run(r1), run(r2)
+    per_row = max((t2 - t1) / max(r2 - r1, 1), 1e-9) if r2 > r1 else t1 / r1
+    fixed = max(t1 - r1 * per_row, 0.0)
+    want = int(max(cores, min(M, (target_s - fixed) / per_row)))
     return max(cores, (want // cores) * cores)
 
 
@@ -195,7 +198,7 @@ def run_reference(args, rank, world):
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit_line(line)
 
 
 # --------------------------------------------------------------------------------------------
@@ -372,10 +375,41 @@ def run_b200(args, rank, world, local_rank):
         line.update(extra)
         if args.gpus == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(wl["cpu"])
-        print(json.dumps(line), flush=True)
+        emit_line(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+class _QuietStdout:
+    """Keeps stdout for the one JSON line: while active, file descriptor 1 points at stderr, so
+    anything a library prints (NCCL's version banner, for one) cannot precede or follow it."""
+
+    def __enter__(self):
+        sys.stdout.flush()
+        self._real = os.dup(1)
+        os.dup2(2, 1)
+        return self
+
+    def emit(self, text: str):
+        os.write(self._real, (text + "\n").encode())
+
+    def __exit__(self, *exc):
+        sys.stdout.flush()
+        os.dup2(self._real, 1)
+        os.close(self._real)
+        return False
+
+
+_OUT = None
+
+
+def emit_line(obj):
+    text = json.dumps(obj)
+    if _OUT is not None:
+        _OUT.emit(text)
+    else:
+        print(text, flush=True)
 
 
 def main():
@@ -390,12 +424,19 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
-        run_reference(args, rank, world)
-        return
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (torchrun --nproc-per-node {args.gpus}); got WORLD_SIZE={world}")
-    run_b200(args, rank, world, local_rank)
+    global _OUT
+    with _QuietStdout() as out:
+        _OUT = out
+        try:
+            if args.impl == "reference":
+                run_reference(args, rank, world)
+                return
+            if world != args.gpus:
+                raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (torchrun --nproc-per-node {args.gpus}); "
+                                 f"got WORLD_SIZE={world}")
+            run_b200(args, rank, world, local_rank)
+        finally:
+            _OUT = None
 
 
 if __name__ == "__main__":

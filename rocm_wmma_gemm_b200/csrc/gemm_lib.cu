@@ -652,10 +652,20 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     // Split-K partials go to this stream's cached f32 workspace, laid out [batch][split][Mk][Nk].
     float*       ws       = nullptr;
     const size_t ws_bytes = split > 1 ? (size_t)p.batch * split * v.M * v.N * sizeof(float) : 0;
+    bool         ws_stream_ordered = false;
     if (split > 1) {
         if (!transposed && v.N % 4) return fail(B200_GEMM_ERR_BAD_CONFIG, "split_k needs N %% 4 == 0 in the kernel view");
-        st = get_workspace(ctx, stream, ws_bytes, &ws);
-        if (st != B200_GEMM_OK) return st;
+        // While the stream is being captured into a graph nothing may be allocated with
+        // cudaMalloc; a stream-ordered allocation becomes part of the graph instead.
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        CUDA_TRY(cudaStreamIsCapturing(stream, &cap));
+        if (cap != cudaStreamCaptureStatusNone) {
+            CUDA_TRY(cudaMallocAsync(reinterpret_cast<void**>(&ws), ws_bytes, stream));
+            ws_stream_ordered = true;
+        } else {
+            st = get_workspace(ctx, stream, ws_bytes, &ws);
+            if (st != B200_GEMM_OK) return st;
+        }
     }
 
     CUtensorMap tmA, tmB, tmD;
@@ -673,7 +683,10 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
             st = encode_map(&tmD, out == OUT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                             v.d, v.N, v.M, p.batch, 64, 32);
     }
-    if (st != B200_GEMM_OK) return st;
+    if (st != B200_GEMM_OK) {
+        if (ws_stream_ordered) cudaFreeAsync(ws, stream);
+        return st;
+    }
 
     const uint32_t smem     = gemm_smem_bytes(bn, (int)cl, cfg.stages, transposed);
     const uint32_t units    = std::min<uint32_t>(gp.num_work, (uint32_t)ctx->sm_count / cl);
@@ -701,6 +714,7 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     }
     g_launches.fetch_add(1, std::memory_order_relaxed);
     if (e != cudaSuccess) {
+        if (ws_stream_ordered) cudaFreeAsync(ws, stream);
         return fail(B200_GEMM_ERR_CUDA, "GEMM kernel launch failed: %s (tile_n=%d stages=%d smem=%u)", cudaGetErrorString(e), bn,
                     cfg.stages, smem);
     }
@@ -716,6 +730,7 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
         }
         g_launches.fetch_add(1, std::memory_order_relaxed);
         e = cudaGetLastError();
+        if (ws_stream_ordered) cudaFreeAsync(ws, stream);
         if (e != cudaSuccess) return fail(B200_GEMM_ERR_CUDA, "split-K reduce launch failed: %s", cudaGetErrorString(e));
     }
     return B200_GEMM_OK;

@@ -14,6 +14,8 @@
 
 #include "ptx_sm100.cuh"
 
+#include <type_traits>
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -49,6 +51,7 @@ struct GemmParams {
     unsigned int* status;  // device status word
     void*    out;          // transposed epilogue only: base of the (Nk x Mk, row-major) output
     uint32_t k_skew;       // work unit w starts its K loop (w * k_skew) k-blocks in (0 = in order)
+    uint32_t stagger;      // 512-wide tiles: k-blocks by which the two column halves are staggered
 };
 
 constexpr int      BLOCK_M        = 128;
@@ -170,6 +173,36 @@ __device__ __forceinline__ void umma_arrive(uint32_t bar)
 {
     if constexpr (CL == 2) ptx::umma_commit_pair(bar, 0x3);
     else ptx::umma_commit(bar);
+}
+
+// Schedule of a 512-wide tile (two 256-column halves that share the staged A' tile).
+// With a stagger of X k-blocks a work unit of nkb k-blocks runs nkb + X steps:
+//   steps [0, X)          half 0 alone on k-blocks 0 .. X-1
+//   steps [X, nkb)        both halves on k-block s (one A' tile feeds two MMAs)
+//   steps [nkb, nkb + X)  half 1 alone on k-blocks 0 .. X-1 (its K order is rotated by X)
+// Half 0 is complete X steps before half 1, so its accumulator drains while half 1 finishes,
+// and half 1 drains under the next tile's half-0-only steps: the tensor pipe does not wait for
+// the epilogue although one tile fills all 512 TMEM columns.  Cost: A' k-blocks 0 .. X-1 are
+// staged twice.
+struct TileStep {
+    uint32_t kb_rel; // k-block relative to the work unit's first
+    uint32_t mask;   // bit h set: column half h takes part
+};
+
+__device__ __forceinline__ TileStep tile_step(uint32_t s, uint32_t nkb, uint32_t stagger)
+{
+    TileStep t;
+    if (s < stagger) {
+        t.kb_rel = s;
+        t.mask   = 1u;
+    } else if (s < nkb) {
+        t.kb_rel = s;
+        t.mask   = 3u;
+    } else {
+        t.kb_rel = s - nkb;
+        t.mask   = 2u;
+    }
+    return t;
 }
 
 template <int OUT>
@@ -301,21 +334,27 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 // a few memory channels.
                 const uint32_t nkb = c.kb1 - c.kb0;
                 const uint32_t rot = p.k_skew ? static_cast<uint32_t>((static_cast<uint64_t>(w) * p.k_skew) % nkb) : 0u;
-                for (uint32_t i = 0; i < nkb; ++i) {
-                    const uint32_t kb = c.kb0 + (i + rot >= nkb ? i + rot - nkb : i + rot);
+                const uint32_t stg_x  = (NSUB == 2) ? min(p.stagger, nkb) : 0u;
+                const uint32_t nsteps = nkb + stg_x;
+                for (uint32_t i = 0; i < nsteps; ++i) {
+                    const TileStep ts   = (NSUB == 2) ? tile_step(i, nkb, stg_x) : TileStep{i, 1u};
+                    const uint32_t rel  = ts.kb_rel + rot >= nkb ? ts.kb_rel + rot - nkb : ts.kb_rel + rot;
+                    const uint32_t kb   = c.kb0 + rel;
+                    const uint32_t nsub = (NSUB == 2) ? __popc(ts.mask) : 1u;
                     ok = bounded_wait(ptx::smem_u32(&s_empty[stage]), phase ^ 1u, &s_abort,
                                       p.status, ST_PRODUCER_WAIT);
                     if (!ok) break;
                     const uint32_t sa = ring + stage * STAGE_BYTES;
                     const uint32_t sb = sa + A_TILE_BYTES;
                     const int32_t  k0 = static_cast<int32_t>(kb * BLOCK_K);
+                    const uint32_t step_bytes = A_TILE_BYTES + nsub * SUB_BYTES; // this CTA's share
                     uint32_t       bar = ptx::smem_u32(&s_full[stage]);
                     if constexpr (CL == 2) {
                         // Rank 0 owns the pair's full barrier and expects both CTAs' bytes.
-                        if (rank == 0) ptx::mbar_expect_tx(bar, 2 * STAGE_BYTES);
+                        if (rank == 0) ptx::mbar_expect_tx(bar, 2 * step_bytes);
                         bar = ptx::mapa_u32(bar, 0);
                     } else {
-                        ptx::mbar_expect_tx(bar, STAGE_BYTES);
+                        ptx::mbar_expect_tx(bar, step_bytes);
                     }
                     if (p.a_mn_major == 0u) {
                         tma_load<CL>(sa, &tmA, bar, k0, am, c.z_in);
@@ -327,6 +366,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     }
 #pragma unroll
                     for (int h = 0; h < NSUB; ++h) {
+                        if (NSUB == 2 && !((ts.mask >> h) & 1u)) continue;
                         const int32_t  bh = bn + h * UMMA_N; // first B' row of sub-tile h
                         const uint32_t sh = sb + h * SUB_BYTES;
                         if (p.b_mn_major == 0u) {
@@ -376,9 +416,65 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             uint32_t       stage = 0, phase = 0, it = 0;
             bool           ok = true;
             for (uint32_t w = unit; ok && w < p.num_work; w += units, ++it) {
-                const WorkCoord c      = decode_work(p, w, BN, BLOCK_M * CL);
-                const uint32_t  buf    = it % NUM_ACC;
-                const uint32_t  aphase = (it / NUM_ACC) & 1u;
+                const WorkCoord c = decode_work(p, w, BN, BLOCK_M * CL);
+                if constexpr (NSUB == 2) {
+                    // Two column halves with their own full / empty barriers (s_tfull[h],
+                    // s_tempty[h]), staggered by stg_x k-blocks: see TileStep.  Three
+                    // straight-line loops (half 0 alone, both, half 1 alone): the MMAs of one
+                    // step must be issued back to back, with no branch between the two halves
+                    // that share an A' tile — a conditional in this loop costs 10 % of the
+                    // kernel's throughput.
+                    const uint32_t nkb    = c.kb1 - c.kb0;
+                    const uint32_t stg_x  = min(p.stagger, nkb);
+                    const uint32_t tphase = it & 1u;
+                    auto step = [&](auto mask_c, uint32_t acc0, uint32_t acc1) -> bool {
+                        constexpr uint32_t MASK = decltype(mask_c)::value;
+                        if (!bounded_wait(ptx::smem_u32(&s_full[stage]), phase, &s_abort, p.status,
+                                          ST_MMA_WAIT_FULL))
+                            return false;
+                        ptx::tc_fence_after();
+                        const uint32_t sa = ring + stage * STAGE_BYTES;
+                        const uint32_t sb = sa + A_TILE_BYTES;
+                        const uint64_t ad = ptx::make_smem_desc(sa, a_lbo, 1024u);
+                        const uint64_t bd = ptx::make_smem_desc(sb, b_lbo, 1024u);
+#pragma unroll
+                        for (uint32_t k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                            if constexpr ((MASK & 1u) != 0u)
+                                ptx::umma_f16<CL>(tmem_base, ad + k * a_kstep, bd + k * b_kstep, p.idesc,
+                                                  (acc0 | k) ? 1u : 0u);
+                            if constexpr ((MASK & 2u) != 0u)
+                                ptx::umma_f16<CL>(tmem_base + UMMA_N, ad + k * a_kstep,
+                                                  bd + (SUB_BYTES >> 4) + k * b_kstep, p.idesc,
+                                                  (acc1 | k) ? 1u : 0u);
+                        }
+                        umma_arrive<CL>(ptx::smem_u32(&s_empty[stage]));
+                        if (++stage == stages) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                        return true;
+                    };
+                    // half 0 starts: its columns must have been drained
+                    ok = bounded_wait<CL == 2>(ptx::smem_u32(&s_tempty[0]), tphase ^ 1u, &s_abort, p.status,
+                                               ST_MMA_WAIT_ACC);
+                    for (uint32_t i = 0; ok && i < stg_x; ++i)
+                        ok = step(std::integral_constant<uint32_t, 1u>{}, i > 0u ? 1u : 0u, 0u);
+                    if (!ok) break;
+                    // half 1 starts
+                    ok = bounded_wait<CL == 2>(ptx::smem_u32(&s_tempty[1]), tphase ^ 1u, &s_abort, p.status,
+                                               ST_MMA_WAIT_ACC);
+                    for (uint32_t i = stg_x; ok && i < nkb; ++i)
+                        ok = step(std::integral_constant<uint32_t, 3u>{}, i > 0u ? 1u : 0u, i > stg_x ? 1u : 0u);
+                    if (!ok) break;
+                    umma_arrive<CL>(ptx::smem_u32(&s_tfull[0])); // half 0 complete
+                    for (uint32_t i = 0; ok && i < stg_x; ++i)
+                        ok = step(std::integral_constant<uint32_t, 2u>{}, 0u, (nkb > stg_x || i > 0u) ? 1u : 0u);
+                    if (!ok) break;
+                    umma_arrive<CL>(ptx::smem_u32(&s_tfull[1])); // half 1 complete
+                    continue;
+                }
+                const uint32_t buf    = it % NUM_ACC;
+                const uint32_t aphase = (it / NUM_ACC) & 1u;
                 ok = bounded_wait<CL == 2>(ptx::smem_u32(&s_tempty[buf]), aphase ^ 1u, &s_abort,
                                            p.status, ST_MMA_WAIT_ACC);
                 if (!ok) break;
@@ -395,12 +491,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     const uint64_t bd = ptx::make_smem_desc(sb, b_lbo, 1024u);
 #pragma unroll
                     for (uint32_t k = 0; k < BLOCK_K / UMMA_K; ++k) {
-#pragma unroll
-                        for (uint32_t h = 0; h < NSUB; ++h) {
-                            ptx::umma_f16<CL>(d_tmem + h * UMMA_N, ad + k * a_kstep,
-                                              bd + h * (SUB_BYTES >> 4) + k * b_kstep, p.idesc,
-                                              (kb > c.kb0 || k > 0u) ? 1u : 0u);
-                        }
+                        ptx::umma_f16<CL>(d_tmem, ad + k * a_kstep, bd + k * b_kstep, p.idesc,
+                                          (kb > c.kb0 || k > 0u) ? 1u : 0u);
                     }
                     // Slot free (in both CTAs of a pair) once these MMAs retire.
                     umma_arrive<CL>(ptx::smem_u32(&s_empty[stage]));
@@ -433,14 +525,22 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             const WorkCoord c      = decode_work(p, w, BN, BLOCK_M * CL);
             const uint32_t  buf    = it % NUM_ACC;
             const uint32_t  aphase = (it / NUM_ACC) & 1u;
-            ok = bounded_wait(ptx::smem_u32(&s_tfull[buf]), aphase, &s_abort, p.status,
+            // A 512-wide tile is drained as two 256-column halves, each published (s_tfull[h])
+            // and handed back (s_tempty[h]) on its own; narrower tiles have one accumulator per
+            // barrier pair.
+#pragma unroll 1
+            for (uint32_t hh = 0; hh < static_cast<uint32_t>(NSUB); ++hh) {
+            const uint32_t bar_i  = (NSUB == 2) ? hh : buf;
+            const uint32_t parity = (NSUB == 2) ? (it & 1u) : aphase;
+            const uint32_t colh   = hh * UMMA_N; // first column of this half within the tile
+            ok = bounded_wait(ptx::smem_u32(&s_tfull[bar_i]), parity, &s_abort, p.status,
                               ST_EPI_WAIT);
             ok = __all_sync(0xffffffffu, ok); // warp-uniform: the TMEM loads below are aligned
             if (!ok) break;
             ptx::tc_fence_after();
             const uint32_t row0     = c.m0 + rank * BLOCK_M + q * 32u;
             const bool     row_live = row0 < p.M;
-            const uint32_t tacc = tmem_base + ((q * 32u) << 16) + buf * ACC_COLS;
+            const uint32_t tacc = tmem_base + ((q * 32u) << 16) + buf * ACC_COLS + colh;
             if constexpr (TR) {
                 // Transposed epilogue: D(i, j) goes to out[j * M + i].  Each lane owns row i, so
                 // for a fixed column j the warp writes 32 consecutive elements: coalesced stores
@@ -481,8 +581,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             uint32_t       n0[32], n1[32]; // raw accumulator words of the chunk in flight
             ptx::tmem_ld_32x32(tacc, n0);
             if constexpr (OUT != OUT_F32) ptx::tmem_ld_32x32(tacc + 32u, n1);
+            constexpr int NCH_H = NCHUNK / NSUB; // chunks per half
 #pragma unroll 1
-            for (int ch = 0; ch < NCHUNK; ++ch) {
+            for (int ch = 0; ch < NCH_H; ++ch) {
                 uint32_t v[32];
                 ptx::tmem_ld_wait(n0);
                 if constexpr (OUT == OUT_F32) {
@@ -496,20 +597,20 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                         v[16 + j] = pack2<OUT>(n1[2 * j], n1[2 * j + 1]);
                     }
                 }
-                if (ch + 1 < NCHUNK) {
+                if (ch + 1 < NCH_H) {
                     ptx::tmem_ld_32x32(tacc + (ch + 1) * CH, n0);
                     if constexpr (OUT != OUT_F32) ptx::tmem_ld_32x32(tacc + (ch + 1) * CH + 32u, n1);
                 }
-                if (ch == NCHUNK - 1) {
-                    // Accumulator fully read: hand it back to the MMA issuer (rank 0).
+                if (ch == NCH_H - 1) {
+                    // Accumulator (half) fully read: hand it back to the MMA issuer (rank 0).
                     ptx::tc_fence_before();
                     __syncwarp();
                     if (lane == 0) {
-                        if constexpr (CL == 2) ptx::mbar_arrive_cluster(ptx::smem_u32(&s_tempty[buf]), 0);
-                        else ptx::mbar_arrive(ptx::smem_u32(&s_tempty[buf]));
+                        if constexpr (CL == 2) ptx::mbar_arrive_cluster(ptx::smem_u32(&s_tempty[bar_i]), 0);
+                        else ptx::mbar_arrive(ptx::smem_u32(&s_tempty[bar_i]));
                     }
                 }
-                const uint32_t col0 = c.n0 + ch * CH;
+                const uint32_t col0 = c.n0 + colh + ch * CH;
                 if (row_live && col0 < p.N) {
                     const uint32_t sbuf = stg + (nstore & 1u) * EPI_BUF_BYTES;
                     // The store that last used this buffer (two stores ago) must have read it.
@@ -530,6 +631,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     ++nstore;
                 }
             }
+            } // halves
         }
         if (lane == 0) ptx::tma_store_wait_all<0>();
     }

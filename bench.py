@@ -39,7 +39,7 @@ LAYOUT_NAMES = ["".join("rc"[x] for x in l) for l in LAYOUTS]
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # DRAM bytes (read + write) of one 8192^3 bf16->f32 launch of gemm_umma_kernel, from the ncu
 # capture summarised in profiles/.
-NCU_DRAM_BYTES_PER_LAUNCH_8192 = 1.360e9  # 1.123 GB read + 0.237 GB write (profiles/gemm_umma_256x512_8192cubed_bf16_f32.md)
+NCU_DRAM_BYTES_PER_LAUNCH_8192 = 1.413e9  # 1.172 GB read + 0.241 GB write (profiles/gemm_umma_256x512_8192cubed_bf16_f32.md)
 
 
 def load_peaks():
@@ -292,8 +292,30 @@ def run_b200(args, rank, world, local_rank):
     total_ms_max = float(t.item())
     value = flops_per_step * args.steps / (total_ms_max * 1e-3) / 1e12
 
-    # ---- optional all-gather of the C slabs (reported beside the headline, not inside it) ----
     extra = {}
+    # ---- N = 1 only: the multi-GPU workload on this one GPU, so that the N > 1 lines (16384^3
+    # column slabs) have a like-for-like single-GPU number next to the headline ----------------
+    if wl["kind"] == "layouts" and world == 1 and not args.no_scaling_base:
+        Mb = Nb = Kb = 16384
+        Ab = (torch.randn(Mb * Kb, device=dev, generator=gen)).to(torch.bfloat16)
+        Bb = (torch.randn(Kb * Nb, device=dev, generator=gen)).to(torch.bfloat16)
+        Cb = torch.empty(Mb * Nb, device=dev, dtype=torch.bfloat16)
+        for _ in range(3):
+            L.gemm(Cb, Ab, Bb, Mb, Nb, Kb, 0, 0, 1)
+        torch.cuda.synchronize()
+        nb = max(3, min(args.steps, 10))
+        b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b0.record()
+        for _ in range(nb):
+            L.gemm(Cb, Ab, Bb, Mb, Nb, Kb, 0, 0, 1)
+        b1.record()
+        torch.cuda.synchronize()
+        extra["scaling_base"] = {"workload": "16384^3 bf16->bf16 GEMM, A row / B col / C row, whole problem on 1 GPU",
+                                 "value": 2.0 * Mb * Nb * Kb * nb / (b0.elapsed_time(b1) * 1e-3) / 1e12, "unit": "TFLOP/s",
+                                 "steps": nb, "note": "single-GPU point of the N>1 workload (N>1 lines shard this problem)"}
+        del Ab, Bb, Cb
+
+    # ---- optional all-gather of the C slabs (reported beside the headline, not inside it) ----
     if wl["kind"] == "slab" and world > 1 and n_local * world == N:
         gathered = torch.empty(world * M * n_local, device=dev, dtype=out_dt)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -419,6 +441,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
+    ap.add_argument("--no-scaling-base", action="store_true", help="skip the 16384^3 single-GPU point (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
     rank = int(os.environ.get("RANK", "0"))

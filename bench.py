@@ -334,6 +334,22 @@ def run_b200(args, rank, world, local_rank):
         extra["with_allgather"] = {"value": flops_per_step * args.steps / (float(tg.item()) * 1e-3) / 1e12,
                                    "unit": "TFLOP/s", "note": "slab GEMM + NCCL all_gather of C slabs ([G][M][N/G]) per step"}
         del gathered
+        # the same exchange overlapped with the compute, row panel by row panel
+        from rocm_wmma_gemm_b200.multi_gpu import ColumnSlabGemm
+        plan = ColumnSlabGemm(M, N, K, 0, 0, 1)
+        for _ in range(2):
+            plan.run_and_gather(C, A, B, panels=4)
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            plan.run_and_gather(C, A, B, panels=4)
+        e1.record()
+        barrier()
+        to = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        dist.all_reduce(to, op=dist.ReduceOp.MAX)
+        extra["with_allgather_overlapped"] = {
+            "value": flops_per_step * args.steps / (float(to.item()) * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "note": "ColumnSlabGemm.run_and_gather: 4 row panels, all-gather of panel p under the GEMM of panel p+1, full C assembled"}
 
     # ---- end to end through the host-buffer entry point ---------------------------------------
     e2e_steps = max(1, min(args.steps, 3))

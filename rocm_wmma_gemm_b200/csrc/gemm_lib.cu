@@ -162,7 +162,9 @@ struct DeviceCtx {
         size_t       bytes;
     };
     std::vector<Workspace> workspaces;
-    // host-buffer path
+    // host-buffer path: compute stream, copy-in / copy-out streams and the events chaining them
+    cudaStream_t h_in = nullptr, h_out = nullptr;
+    cudaEvent_t  h_ev_in[16] = {}, h_ev_done[16] = {}, h_ev_b = nullptr;
     cudaStream_t h_stream = nullptr;
     void*        h_buf[3] = {nullptr, nullptr, nullptr};
     size_t       h_cap[3] = {0, 0, 0};
@@ -1035,6 +1037,75 @@ extern "C" int b200_gemm_host(int types, void* C, const void* A, const void* B, 
         }
     }
     cudaStream_t s = ctx->h_stream;
+
+    // Large single problems are pipelined: the operand that is not chunked goes up first, then
+    // chunks of the other operand (rows of A, or columns of B) are copied in, multiplied and
+    // their slice of C copied out on three streams, so the upload, the GEMMs and the download
+    // overlap (PCIe is full duplex).  Every chunk is stored densely on the device, so each
+    // chunk is an ordinary dense GEMM whatever the layouts.
+    const bool   by_rows  = M >= N;
+    const size_t dim      = by_rows ? M : N;
+    size_t       nchunks  = std::min<size_t>(8, dim / 512);
+    if (batch_count == 1 && nchunks >= 2 && bytes[0] + bytes[1] + bytes[2] >= (32u << 20) && K > 0) {
+        {
+            std::lock_guard<std::mutex> lock(g_mutex);
+            if (!ctx->h_in) {
+                CUDA_TRY(cudaStreamCreateWithFlags(&ctx->h_in, cudaStreamNonBlocking));
+                CUDA_TRY(cudaStreamCreateWithFlags(&ctx->h_out, cudaStreamNonBlocking));
+                CUDA_TRY(cudaEventCreateWithFlags(&ctx->h_ev_b, cudaEventDisableTiming));
+                for (int i = 0; i < 16; ++i) {
+                    CUDA_TRY(cudaEventCreateWithFlags(&ctx->h_ev_in[i], cudaEventDisableTiming));
+                    CUDA_TRY(cudaEventCreateWithFlags(&ctx->h_ev_done[i], cudaEventDisableTiming));
+                }
+            }
+        }
+        const size_t step = ((dim + nchunks - 1) / nchunks + 255) / 256 * 256;
+        char*        dA   = static_cast<char*>(ctx->h_buf[0]);
+        char*        dB   = static_cast<char*>(ctx->h_buf[1]);
+        char*        dC   = static_cast<char*>(ctx->h_buf[2]);
+        const char*  hA   = static_cast<const char*>(A);
+        const char*  hB   = static_cast<const char*>(B);
+        char*        hC   = static_cast<char*>(C);
+        // the whole of the operand that is not chunked
+        if (by_rows) CUDA_TRY(cudaMemcpyAsync(dB, hB, bytes[1], cudaMemcpyHostToDevice, ctx->h_in));
+        else CUDA_TRY(cudaMemcpyAsync(dA, hA, bytes[0], cudaMemcpyHostToDevice, ctx->h_in));
+        size_t ci = 0;
+        for (size_t c0 = 0; c0 < dim; c0 += step, ++ci) {
+            const size_t cn = std::min(step, dim - c0);
+            if (by_rows) { // rows [c0, c0 + cn) of A and C
+                char* dAc = dA + c0 * K * 2;
+                if (layout_a == 0) CUDA_TRY(cudaMemcpyAsync(dAc, hA + c0 * K * 2, cn * K * 2, cudaMemcpyHostToDevice, ctx->h_in));
+                else CUDA_TRY(cudaMemcpy2DAsync(dAc, cn * 2, hA + c0 * 2, M * 2, cn * 2, K, cudaMemcpyHostToDevice, ctx->h_in));
+            } else { // columns [c0, c0 + cn) of B and C
+                char* dBc = dB + c0 * K * 2;
+                if (layout_b == 1) CUDA_TRY(cudaMemcpyAsync(dBc, hB + c0 * K * 2, cn * K * 2, cudaMemcpyHostToDevice, ctx->h_in));
+                else CUDA_TRY(cudaMemcpy2DAsync(dBc, cn * 2, hB + c0 * 2, N * 2, cn * 2, K, cudaMemcpyHostToDevice, ctx->h_in));
+            }
+            CUDA_TRY(cudaEventRecord(ctx->h_ev_in[ci], ctx->h_in));
+            CUDA_TRY(cudaStreamWaitEvent(s, ctx->h_ev_in[ci], 0));
+            char* dCc = dC + (by_rows ? c0 * N : c0 * M) * out_sz;
+            const Problem cp = by_rows ? Problem{types, dCc, dA + c0 * K * 2, dB, cn, N, K, 1, layout_c, layout_a, layout_b}
+                                       : Problem{types, dCc, dA, dB + c0 * K * 2, M, cn, K, 1, layout_c, layout_a, layout_b};
+            st = run_gemm(cp, s, nullptr);
+            if (st != B200_GEMM_OK) {
+                cudaDeviceSynchronize();
+                return st;
+            }
+            CUDA_TRY(cudaEventRecord(ctx->h_ev_done[ci], s));
+            CUDA_TRY(cudaStreamWaitEvent(ctx->h_out, ctx->h_ev_done[ci], 0));
+            if (by_rows) {
+                if (layout_c == 0) CUDA_TRY(cudaMemcpyAsync(hC + c0 * N * out_sz, dCc, cn * N * out_sz, cudaMemcpyDeviceToHost, ctx->h_out));
+                else CUDA_TRY(cudaMemcpy2DAsync(hC + c0 * out_sz, M * out_sz, dCc, cn * out_sz, cn * out_sz, N, cudaMemcpyDeviceToHost, ctx->h_out));
+            } else {
+                if (layout_c == 1) CUDA_TRY(cudaMemcpyAsync(hC + c0 * M * out_sz, dCc, M * cn * out_sz, cudaMemcpyDeviceToHost, ctx->h_out));
+                else CUDA_TRY(cudaMemcpy2DAsync(hC + c0 * out_sz, N * out_sz, dCc, cn * out_sz, cn * out_sz, M, cudaMemcpyDeviceToHost, ctx->h_out));
+            }
+        }
+        CUDA_TRY(cudaStreamSynchronize(ctx->h_out));
+        CUDA_TRY(cudaStreamSynchronize(s));
+        return B200_GEMM_OK;
+    }
+
     if (bytes[0]) CUDA_TRY(cudaMemcpyAsync(ctx->h_buf[0], A, bytes[0], cudaMemcpyHostToDevice, s));
     if (bytes[1]) CUDA_TRY(cudaMemcpyAsync(ctx->h_buf[1], B, bytes[1], cudaMemcpyHostToDevice, s));
     const Problem dp{types, ctx->h_buf[2], ctx->h_buf[0], ctx->h_buf[1], M, N, K, batch_count, layout_c, layout_a, layout_b};

@@ -59,16 +59,63 @@ class ColumnSlabGemm:
         self._loader = None
 
     # -- compute: no collective ------------------------------------------------------------------
-    def run(self, C_slab, A, B_slab, stream=None) -> None:
-        if self.n_count == 0:
-            return
+    def _local(self, C, A, B, rows, stream=None) -> None:
+        """The local GEMM on `rows` rows of A and of the C slab."""
         if self._gemm is not None:
-            self._gemm(C_slab, A, B_slab, self.M, self.n_count, self.K, self.layout_c, self.layout_a, self.layout_b)
+            self._gemm(C, A, B, rows, self.n_count, self.K, self.layout_c, self.layout_a, self.layout_b)
             return
         if self._loader is None:
             self._loader = _loader()
-        self._loader.gemm(C_slab, A, B_slab, self.M, self.n_count, self.K, self.layout_c, self.layout_a,
-                          self.layout_b, stream=stream)
+        self._loader.gemm(C, A, B, rows, self.n_count, self.K, self.layout_c, self.layout_a, self.layout_b,
+                          stream=stream)
+
+    def run(self, C_slab, A, B_slab, stream=None) -> None:
+        if self.n_count == 0:
+            return
+        self._local(C_slab, A, B_slab, self.M, stream)
+
+    # -- compute overlapped with the exchange ----------------------------------------------------
+    def run_and_gather(self, C_slab: torch.Tensor, A: torch.Tensor, B_slab: torch.Tensor, panels: int = 4) -> torch.Tensor:
+        """run() + gather() with the all-gather of row panel p in flight while panel p + 1 is
+        being computed (the GEMM of a panel and the collective of the previous one run on
+        different streams).  Needs row-major A and C (row panels are then contiguous) and equal
+        slabs; anything else takes the plain run() then gather() route.  Returns the full C."""
+        widths = [c for _, c in self.slabs]
+        even = len(set(widths)) == 1 and widths[0] * self.world == self.N
+        if self.world == 1 or self.layout_a != 0 or self.layout_c != 0 or not even or panels < 2:
+            self.run(C_slab, A, B_slab)
+            return self.gather(C_slab)
+        M, K, nl, G = self.M, self.K, self.n_count, self.world
+        step = -(-M // panels)
+        step = -(-step // 256) * 256
+        on_gpu = C_slab.is_cuda
+        if on_gpu and getattr(self, "_comm", None) is None:
+            self._comm = torch.cuda.Stream()
+        Cf, Af = C_slab.reshape(-1), A.reshape(-1)
+        full = torch.empty(M * self.N, dtype=Cf.dtype, device=Cf.device)
+        pending = []
+        for r0 in range(0, M, step):
+            r1 = min(M, r0 + step)
+            Cp = Cf[r0 * nl: r1 * nl]
+            self._local(Cp, Af[r0 * K: r1 * K], B_slab, r1 - r0)
+            stage = torch.empty(G * (r1 - r0) * nl, dtype=Cf.dtype, device=Cf.device)
+            if on_gpu:
+                done = torch.cuda.Event()
+                done.record()
+                with torch.cuda.stream(self._comm):
+                    self._comm.wait_event(done)
+                    work = dist.all_gather_into_tensor(stage.view(torch.uint8), Cp.view(torch.uint8), group=self.group,
+                                                       async_op=True)
+            else:
+                work = dist.all_gather_into_tensor(stage.view(torch.uint8), Cp.view(torch.uint8), group=self.group,
+                                                   async_op=True)
+            pending.append((work, stage, r0, r1))
+        rows = full.view(M, G, nl)
+        for work, stage, r0, r1 in pending:
+            work.wait()
+            # [rank][row][col] -> rows r0..r1 of the full matrix, slab by slab
+            rows[r0:r1].copy_(stage.view(G, r1 - r0, nl).permute(1, 0, 2))
+        return full
 
     # -- optional exchange -----------------------------------------------------------------------
     def gather(self, C_slab: torch.Tensor) -> torch.Tensor:

@@ -47,8 +47,13 @@ def _worker(rank, world, port, M, N, K, lc, la, lb, types, align, result_file):
     B_slab = torch.from_numpy(_store(B_full[:, n0:n0 + nl], lb).view(np.int16))
     out_dt = torch.float32 if types in (1, 3) else torch.int16
     C_slab = torch.zeros(M * max(nl, 1), dtype=out_dt)
-    plan.run(C_slab, torch.from_numpy(A.view(np.int16)), B_slab)
+    A_t = torch.from_numpy(A.view(np.int16))
+    plan.run(C_slab, A_t, B_slab)
     full = plan.gather(C_slab[: M * nl])
+    # the overlapped route must give the same matrix (it falls back where it does not apply)
+    C2 = torch.zeros_like(C_slab)
+    full2 = plan.run_and_gather(C2, A_t, B_slab, panels=3)
+    assert torch.equal(full2, full), "run_and_gather differs from run + gather"
     if rank == 1 % world:
         np.save(result_file, full.numpy())
     dist.barrier()
@@ -57,6 +62,7 @@ def _worker(rank, world, port, M, N, K, lc, la, lb, types, align, result_file):
 
 @pytest.mark.parametrize("M,N,K,lc,la,lb,types,align", [
     (48, 512, 64, 0, 0, 1, 3, 256),   # the benchmark's layout: A row, B col, C row; even slabs
+    (600, 512, 32, 0, 0, 1, 2, 256),  # several row panels through the overlapped route
     (40, 512, 32, 1, 1, 0, 0, 256),   # column-major C: slabs concatenate
     (24, 1000, 48, 0, 0, 0, 1, 256),  # ragged: slabs of 512 and 488 columns
     (16, 200, 32, 1, 0, 1, 2, 256),   # fewer column groups than ranks: rank 1 owns nothing

@@ -337,18 +337,29 @@ def run_b200(args, rank, world, local_rank):
         # the same exchange overlapped with the compute, row panel by row panel
         from rocm_wmma_gemm_b200.multi_gpu import ColumnSlabGemm
         plan = ColumnSlabGemm(M, N, K, 0, 0, 1)
-        for _ in range(2):
-            plan.run_and_gather(C, A, B, panels=4)
-        barrier()
-        e0.record()
-        for _ in range(args.steps):
-            plan.run_and_gather(C, A, B, panels=4)
-        e1.record()
-        barrier()
-        to = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
-        dist.all_reduce(to, op=dist.ReduceOp.MAX)
-        extra["with_allgather_overlapped"] = {
-            "value": flops_per_step * args.steps / (float(to.item()) * 1e-3) / 1e12, "unit": "TFLOP/s",
+
+        def timed(fn):
+            for _ in range(2):
+                fn()
+            barrier()
+            e0.record()
+            for _ in range(args.steps):
+                fn()
+            e1.record()
+            barrier()
+            tt = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            return flops_per_step * args.steps / (float(tt.item()) * 1e-3) / 1e12
+
+        def sequential():
+            plan.run(C, A, B)
+            return plan.gather(C)
+
+        extra["with_full_c_sequential"] = {
+            "value": timed(sequential), "unit": "TFLOP/s",
+            "note": "ColumnSlabGemm.run then .gather: slab GEMM, all-gather, slabs interleaved into the row-major M x N matrix"}
+        extra["with_full_c_overlapped"] = {
+            "value": timed(lambda: plan.run_and_gather(C, A, B, panels=4)), "unit": "TFLOP/s",
             "note": "ColumnSlabGemm.run_and_gather: 4 row panels, all-gather of panel p under the GEMM of panel p+1, full C assembled"}
 
     # ---- end to end through the host-buffer entry point ---------------------------------------

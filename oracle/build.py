@@ -19,7 +19,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ORACLE_LIB = os.path.join(HERE, "liboracle_gemm.so")
 REF_DIR = os.path.join(HERE, "_ref")
 REF_LIB = os.path.join(REF_DIR, "libref_hgemm.so")
-REFERENCE_ROOT = os.environ.get("ROCM_WMMA_GEMM_REFERENCE", "/root/reference")
+# The reference checkout: $ROCM_WMMA_GEMM_REFERENCE, else a directory `reference` beside this repository.
+REFERENCE_ROOT = os.environ.get("ROCM_WMMA_GEMM_REFERENCE",
+                                os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference"))
 CUDA_INCLUDE = os.environ.get("CUDA_INCLUDE", "/usr/local/cuda/include")
 
 

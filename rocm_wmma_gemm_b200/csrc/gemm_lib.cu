@@ -150,7 +150,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 struct DeviceCtx {
-    bool          ready    = false;
+    std::atomic<bool> ready{false}; // set last, read first: initialised contexts skip the lock
     int           sm_count = 0;
     int           pair_units[3] = {0, 0, 0}; // co-resident CTA pairs for tile_n 128 / 256 / 512 (0 = not asked yet)
     unsigned int* d_status = nullptr;
@@ -225,9 +225,13 @@ static int get_ctx(DeviceCtx** out)
         return fail(B200_GEMM_ERR_NO_DEVICE, "no CUDA device: %s", cudaGetErrorString(e));
     if (dev < 0 || dev >= k_max_devices)
         return fail(B200_GEMM_ERR_NO_DEVICE, "device ordinal %d out of range", dev);
+    DeviceCtx& c = g_ctx[dev];
+    if (c.ready.load(std::memory_order_acquire)) {
+        *out = &c;
+        return B200_GEMM_OK;
+    }
     std::lock_guard<std::mutex> lock(g_mutex);
-    DeviceCtx&                  c = g_ctx[dev];
-    if (!c.ready) {
+    if (!c.ready.load(std::memory_order_relaxed)) {
         cudaDeviceProp prop;
         CUDA_TRY(cudaGetDeviceProperties(&prop, dev));
         if (prop.major != 10)
@@ -255,7 +259,7 @@ static int get_ctx(DeviceCtx** out)
         CUDA_TRY((set_smem_attr_narrow<32>()));
         CUDA_TRY((set_smem_attr_narrow<64>()));
         CUDA_TRY((set_smem_attr_narrow<128>()));
-        c.ready = true;
+        c.ready.store(true, std::memory_order_release);
     }
     *out = &c;
     return B200_GEMM_OK;
@@ -427,12 +431,20 @@ static void legalize(b200_gemm_config& c, const View& v, uint32_t* kb_per_split)
 // replaces the table's choice for every call that does not pass an explicit config.
 static bool env_config(b200_gemm_config* out)
 {
-    const char* e = getenv("B200_GEMM_CONFIG");
-    if (!e || !*e) return false;
-    b200_gemm_config c;
-    if (sscanf(e, "%d,%d,%d,%d,%d,%d", &c.tile_m, &c.tile_n, &c.stages, &c.cluster, &c.split_k, &c.raster) != 6)
-        return false;
-    *out = c;
+    // Parsed once, at the first call: the environment is not re-read on the hot path.
+    static const struct Parsed {
+        bool             set = false;
+        b200_gemm_config cfg{};
+        Parsed()
+        {
+            const char* e = getenv("B200_GEMM_CONFIG");
+            set = e && *e &&
+                  sscanf(e, "%d,%d,%d,%d,%d,%d", &cfg.tile_m, &cfg.tile_n, &cfg.stages, &cfg.cluster, &cfg.split_k,
+                         &cfg.raster) == 6;
+        }
+    } parsed;
+    if (!parsed.set) return false;
+    *out = parsed.cfg;
     return true;
 }
 
@@ -652,9 +664,8 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     // takes to drain: about 5.5k cycles for f32 output, 3.3k for 16-bit, at 512 cycles per k-block.
     gp.stagger = 0;
     if (bn == 512) {
-        uint32_t want = (split > 1 || out == OUT_F32) ? 12u : 8u;
-        if (const char* e = getenv("B200_GEMM_STAGGER")) want = (uint32_t)atoi(e);
-        gp.stagger = std::min<uint32_t>(want, kb_per_split / 2);
+        const uint32_t want = (split > 1 || out == OUT_F32) ? 12u : 8u;
+        gp.stagger          = std::min<uint32_t>(want, kb_per_split / 2);
     }
     // Streaming (HBM-bound) views rotate the K order per work unit; see the producer.
     const bool streaming = narrow || std::min(v.M, v.N) <= 256;

@@ -315,3 +315,42 @@ def test_host_buffer_entry_point_pipelined(M, N, K):
     ref = oracle.hgemm_select(types, A, B, M, N, K, 0, la, lb, rows=rows)
     gl = got.reshape(M, N) if lc == 0 else got.reshape(N, M).T
     assert np.abs(gl[rows] - ref.reshape(M, N)[rows]).max() <= 1e-3
+
+
+def test_concurrent_streams_and_threads():
+    """The library keeps no per-call global state: four host threads, each on its own stream,
+    run split-K and plain GEMMs at the same time (split-K workspaces are per stream)."""
+    import threading
+    M, N, K = 256, 768, 2048
+    A, B = seeded(M, N, K, 0, 1, True)
+    ref = oracle.hgemm(3, A, B, M, N, K, 0, 0, 1)
+    dA, dB = to_device(A), to_device(B)
+    torch.cuda.synchronize()
+    results, errors = {}, []
+
+    def work(i):
+        try:
+            st = torch.cuda.Stream()
+            l = g.loader()
+            outs = []
+            with torch.cuda.stream(st):
+                for rep in range(6):
+                    C = torch.full((M * N,), float("nan"), device="cuda")
+                    cfg = g.GemmConfig(128, 128, 4, 1, 1 + (i + rep) % 4, 0)
+                    l.gemm(C, dA, dB, M, N, K, 0, 0, 1, stream=st, config=cfg)
+                    outs.append(C)
+            st.synchronize()
+            results[i] = [c.cpu().numpy() for c in outs]
+        except Exception as ex:  # surfaced in the main thread
+            errors.append(ex)
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    assert g.device_status() == 0
+    for i in range(4):
+        for out in results[i]:
+            check_parity(3, out, ref, K, SIGMA_UNIFORM, M, N, 0)

@@ -337,7 +337,7 @@ def test_concurrent_streams_and_threads():
                 for rep in range(6):
                     C = torch.full((M * N,), float("nan"), device="cuda")
                     cfg = g.GemmConfig(128, 128, 4, 1, 1 + (i + rep) % 4, 0)
-                    l.gemm(C, dA, dB, M, N, K, 0, 0, 1, stream=st, config=cfg)
+                    l.gemm(C, dA, dB, M, N, K, 0, 0, 1, stream=st, config=cfg, types=3)
                     outs.append(C)
             st.synchronize()
             results[i] = [c.cpu().numpy() for c in outs]

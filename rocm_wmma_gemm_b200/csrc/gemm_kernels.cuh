@@ -52,12 +52,16 @@ struct GemmParams {
     void*    out;          // transposed epilogue only: base of the (Nk x Mk, row-major) output
     uint32_t k_skew;       // work unit w starts its K loop (w * k_skew) k-blocks in (0 = in order)
     uint32_t stagger;      // 512-wide tiles: k-blocks by which the two column halves are staggered
+    uint32_t bm;           // transposed epilogue only: rows of A' per tile ("slab" height, 8 .. 128)
+    uint32_t kc;           // transposed epilogue only: k-blocks per ring slot (1, 2 or 4)
+    uint32_t k4d;          // transposed epilogue only: K-major operands use the 4-D (chunked K) maps
 };
 
 constexpr int      BLOCK_M        = 128;
 constexpr int      BLOCK_K        = 64; // 64 x 2 B = one 128-byte swizzle row
 constexpr int      UMMA_K         = 16;
-constexpr int      MAX_STAGES     = 12;
+constexpr int      MAX_STAGES     = 12; // ring depth of the staged-epilogue kernels
+constexpr int      MAX_SLAB_STAGES = 24; // ring depth of the transposed-epilogue (slab) kernels
 constexpr int      GEMM_THREADS   = 192; // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
 constexpr uint32_t A_TILE_BYTES   = BLOCK_M * BLOCK_K * 2;
 constexpr uint32_t EPI_BUF_BYTES  = 32 * 128; // one warp's 32 rows x 128 B
@@ -75,6 +79,31 @@ __host__ __device__ constexpr uint32_t stage_bytes(int bn, int cluster)
 __host__ __device__ constexpr uint32_t gemm_smem_bytes(int bn, int cluster, int stages, bool transposed = false)
 {
     return static_cast<uint32_t>(stages) * stage_bytes(bn, cluster) + (transposed ? 0u : EPI_BYTES) + 1024;
+}
+
+// Transposed-epilogue kernels stage `bm` <= 128 rows of A' per slot (a "slab"): the MMA still
+// reads 128 rows, so the ring is followed by the slack the last slot's read runs into.
+constexpr uint32_t SLAB_SMEM_LIMIT = 232448u - 1024u; // 227 KiB minus the static barriers
+// A slot holds `kc` consecutive k-blocks of both operands (one TMA instruction per operand
+// fetches all of them: the per-slot barrier and issue work is amortised over kc k-blocks).
+__host__ __device__ constexpr uint32_t slab_stage_bytes(int bm, int bn, int kc)
+{
+    return static_cast<uint32_t>(kc) * static_cast<uint32_t>(bm + bn) * BLOCK_K * 2;
+}
+// The MMA reads 128 rows of A' whatever the slab height, i.e. up to 16 KiB (K-major) or kc x 8 KiB
+// (a 64-row M-major slab) past the last slot: the ring is followed by that much slack.
+__host__ __device__ constexpr uint32_t slab_slack_bytes(int kc)
+{
+    return kc * 8192u > 16384u ? kc * 8192u : 16384u;
+}
+__host__ __device__ constexpr uint32_t slab_smem_bytes(int bm, int bn, int kc, int stages)
+{
+    return static_cast<uint32_t>(stages) * slab_stage_bytes(bm, bn, kc) + slab_slack_bytes(kc) + 1024;
+}
+__host__ __device__ constexpr int slab_max_stages(int bm, int bn, int kc)
+{
+    int s = static_cast<int>((SLAB_SMEM_LIMIT - 1024u - slab_slack_bytes(kc)) / slab_stage_bytes(bm, bn, kc));
+    return s > MAX_SLAB_STAGES ? MAX_SLAB_STAGES : s;
 }
 
 // Deepest ring that fits the 227 KiB a CTA may use (static barriers included).
@@ -96,14 +125,22 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity,
         if constexpr (CLUSTER_SCOPE) return ptx::mbar_try_wait_cluster(bar, parity);
         else return ptx::mbar_try_wait(bar, parity);
     };
-    if (try_wait()) return true;
-    const uint64_t t0    = ptx::global_timer_ns();
-    uint32_t       spins = 0;
+    // The common case is a short wait: try_wait itself blocks for a while, so the timer (a slow
+    // read) and the abort flag are only looked at every 128 failed attempts, and the deadline
+    // starts at the first look.
+    if constexpr (!CLUSTER_SCOPE) {
+        if (ptx::mbar_test_wait(bar, parity)) return true; // already complete: no blocking wait
+    }
+    uint64_t t0    = 0;
+    uint32_t spins = 0;
     while (true) {
         if (try_wait()) return true;
-        if ((++spins & 31u) == 0u) {
+        if ((++spins & 127u) == 0u) {
             if (*s_abort != 0u) return false;
-            if (ptx::global_timer_ns() - t0 > WAIT_LIMIT_NS) {
+            const uint64_t now = ptx::global_timer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > WAIT_LIMIT_NS) {
                 *s_abort = 1u;
                 atomicOr(status, code);
                 return false;
@@ -272,8 +309,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     // (an MN-major B' is loaded in 64-row boxes: the host only picks BN >= 64 * CL for it)
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t s_full[MAX_STAGES];
-    __shared__ __align__(8) uint64_t s_empty[MAX_STAGES];
+    __shared__ __align__(8) uint64_t s_full[TR ? MAX_SLAB_STAGES : MAX_STAGES];
+    __shared__ __align__(8) uint64_t s_empty[TR ? MAX_SLAB_STAGES : MAX_STAGES];
     __shared__ __align__(8) uint64_t s_tfull[2];
     __shared__ __align__(8) uint64_t s_tempty[2];
     __shared__ __align__(8) uint64_t s_drain;
@@ -288,8 +325,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     const uint32_t unit   = blockIdx.x / CL;                          // persistent worker index
     const uint32_t units  = gridDim.x / CL;
 
+    // Bytes of A' per ring slot and slot pitch: compile-time for the staged epilogue; the
+    // transposed variant stages p.bm (a multiple of 8, <= 128) rows of A' per slot.
+    // A slot of the transposed variant holds kc k-blocks: [A' k-block 0 .. kc-1][B' k-block 0 .. kc-1].
+    const uint32_t kc      = TR ? p.kc : 1u;
+    const uint32_t a_bytes = TR ? p.bm * (BLOCK_K * 2u) : A_TILE_BYTES;
+    const uint32_t pitch   = TR ? kc * (a_bytes + B_TILE_BYTES) : STAGE_BYTES;
+    const uint32_t tile_m  = TR ? p.bm : static_cast<uint32_t>(BLOCK_M * CL);
+
     const uint32_t ring = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u; // ring of operand tiles
-    const uint32_t epi  = ring + stages * STAGE_BYTES;                // epilogue staging (unused when TR)
+    const uint32_t epi  = ring + stages * pitch;                      // epilogue staging (unused when TR)
 
     if (tid == 0) {
         ptx::prefetch_tensormap(&tmA);
@@ -318,14 +363,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     }
     ptx::tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
+    // Split-K: let the reduction pass be scheduled now; it waits for this grid to complete.
+    if (p.split_k > 1u) ptx::grid_dep_launch();
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        if (ptx::elect_one()) {
             uint32_t stage = 0, phase = 0, issued = 0;
             bool     ok = true;
             for (uint32_t w = unit; ok && w < p.num_work; w += units) {
-                const WorkCoord c  = decode_work(p, w, BN, BLOCK_M * CL);
+                const WorkCoord c  = decode_work(p, w, BN, tile_m);
                 const int32_t   am = static_cast<int32_t>(c.m0 + rank * BLOCK_M);
                 const int32_t   bn = static_cast<int32_t>(c.n0 + rank * SUB_ROWS);
                 // Streaming (HBM-bound) problems rotate each work unit's K order so that the CTAs
@@ -333,6 +380,47 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 // are a power of two apart, and same-offset reads from thousands of rows land on
                 // a few memory channels.
                 const uint32_t nkb = c.kb1 - c.kb0;
+                if constexpr (TR) {
+                    // Slab variant: one slot = kc k-blocks of A' (p.bm rows) and of B' (BN rows),
+                    // one TMA instruction per operand (per 64-row half for an MN-major operand).
+                    // Boxes that reach past K read zeros, so a ragged last slot needs no care.
+                    const uint32_t nst  = (nkb + kc - 1u) / kc;
+                    const uint32_t rot  = p.k_skew ? static_cast<uint32_t>((static_cast<uint64_t>(w) * p.k_skew) % nst) : 0u;
+                    const uint32_t half = kc * (64u * BLOCK_K * 2u); // bytes of one 64-row half of an MN-major operand
+                    for (uint32_t i = 0; i < nst; ++i) {
+                        const uint32_t rel = i + rot >= nst ? i + rot - nst : i + rot;
+                        const int32_t  kb  = static_cast<int32_t>(c.kb0 + rel * kc);
+                        const int32_t  k0  = kb * BLOCK_K;
+                        ok = bounded_wait(ptx::smem_u32(&s_empty[stage]), phase ^ 1u, &s_abort,
+                                          p.status, ST_PRODUCER_WAIT);
+                        if (!ok) break;
+                        const uint32_t sa  = ring + stage * pitch;
+                        const uint32_t sb  = sa + kc * a_bytes;
+                        const uint32_t bar = ptx::smem_u32(&s_full[stage]);
+                        ptx::mbar_expect_tx(bar, pitch);
+                        if (p.a_mn_major == 0u) {
+                            if (p.k4d) ptx::tma_load_4d(sa, &tmA, bar, 0, am, kb, c.z_in);
+                            else ptx::tma_load_3d(sa, &tmA, bar, k0, am, c.z_in);
+                        } else {
+                            ptx::tma_load_3d(sa, &tmA, bar, am, k0, c.z_in);
+                            if (p.bm > 64u) ptx::tma_load_3d(sa + half, &tmA, bar, am + 64, k0, c.z_in);
+                        }
+                        if (p.b_mn_major == 0u) {
+                            if (p.k4d) ptx::tma_load_4d(sb, &tmB, bar, 0, bn, kb, c.z_in);
+                            else ptx::tma_load_3d(sb, &tmB, bar, k0, bn, c.z_in);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < SUB_ROWS / 64; ++j)
+                                ptx::tma_load_3d(sb + j * half, &tmB, bar, bn + j * 64, k0, c.z_in);
+                        }
+                        ++issued;
+                        if (++stage == stages) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                    }
+                    continue;
+                }
                 const uint32_t rot = p.k_skew ? static_cast<uint32_t>((static_cast<uint64_t>(w) * p.k_skew) % nkb) : 0u;
                 const uint32_t stg_x  = (NSUB == 2) ? min(p.stagger, nkb) : 0u;
                 const uint32_t nsteps = nkb + stg_x;
@@ -344,10 +432,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     ok = bounded_wait(ptx::smem_u32(&s_empty[stage]), phase ^ 1u, &s_abort,
                                       p.status, ST_PRODUCER_WAIT);
                     if (!ok) break;
-                    const uint32_t sa = ring + stage * STAGE_BYTES;
-                    const uint32_t sb = sa + A_TILE_BYTES;
+                    const uint32_t sa = ring + stage * pitch;
+                    const uint32_t sb = sa + a_bytes;
                     const int32_t  k0 = static_cast<int32_t>(kb * BLOCK_K);
-                    const uint32_t step_bytes = A_TILE_BYTES + nsub * SUB_BYTES; // this CTA's share
+                    const uint32_t step_bytes = a_bytes + nsub * SUB_BYTES; // this CTA's share
                     uint32_t       bar = ptx::smem_u32(&s_full[stage]);
                     if constexpr (CL == 2) {
                         // Rank 0 owns the pair's full barrier and expects both CTAs' bytes.
@@ -406,7 +494,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0 && rank == 0) {
+        if (ptx::elect_one() && rank == 0) {
             // K-major swizzled tiles ignore the leading offset (canonical value: 16 bytes).
             const uint32_t a_lbo   = p.a_mn_major ? 64u * BLOCK_K * 2u : 16u;
             const uint32_t b_lbo   = p.b_mn_major ? 64u * BLOCK_K * 2u : 16u;
@@ -416,7 +504,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             uint32_t       stage = 0, phase = 0, it = 0;
             bool           ok = true;
             for (uint32_t w = unit; ok && w < p.num_work; w += units, ++it) {
-                const WorkCoord c = decode_work(p, w, BN, BLOCK_M * CL);
+                const WorkCoord c = decode_work(p, w, BN, tile_m);
                 if constexpr (NSUB == 2) {
                     // Two column halves with their own full / empty barriers (s_tfull[h],
                     // s_tempty[h]), staggered by stg_x k-blocks: see TileStep.  Three
@@ -433,8 +521,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                                           ST_MMA_WAIT_FULL))
                             return false;
                         ptx::tc_fence_after();
-                        const uint32_t sa = ring + stage * STAGE_BYTES;
-                        const uint32_t sb = sa + A_TILE_BYTES;
+                        const uint32_t sa = ring + stage * pitch;
+                        const uint32_t sb = sa + a_bytes;
                         const uint64_t ad = ptx::make_smem_desc(sa, a_lbo, 1024u);
                         const uint64_t bd = ptx::make_smem_desc(sb, b_lbo, 1024u);
 #pragma unroll
@@ -480,13 +568,47 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 if (!ok) break;
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * ACC_COLS;
+                if constexpr (TR) {
+                    // kc k-blocks per slot; see the producer for the slot layout.
+                    const uint32_t nst    = (c.kb1 - c.kb0 + kc - 1u) / kc;
+                    const uint32_t half   = kc * (64u * BLOCK_K * 2u);
+                    const uint32_t a_blk  = p.a_mn_major ? 64u * BLOCK_K * 2u : a_bytes;
+                    const uint32_t b_blk  = p.b_mn_major ? 64u * BLOCK_K * 2u : B_TILE_BYTES;
+                    const uint32_t a_lbo2 = p.a_mn_major ? half : 16u;
+                    const uint32_t b_lbo2 = p.b_mn_major ? half : 16u;
+                    for (uint32_t i = 0; i < nst; ++i) {
+                        ok = bounded_wait(ptx::smem_u32(&s_full[stage]), phase, &s_abort, p.status,
+                                          ST_MMA_WAIT_FULL);
+                        if (!ok) break;
+                        ptx::tc_fence_after();
+                        const uint32_t sa = ring + stage * pitch;
+                        const uint32_t sb = sa + kc * a_bytes;
+                        for (uint32_t c2 = 0; c2 < kc; ++c2) {
+                            const uint64_t ad = ptx::make_smem_desc(sa + c2 * a_blk, a_lbo2, 1024u);
+                            const uint64_t bd = ptx::make_smem_desc(sb + c2 * b_blk, b_lbo2, 1024u);
+#pragma unroll
+                            for (uint32_t k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                                ptx::umma_f16<CL>(d_tmem, ad + k * a_kstep, bd + k * b_kstep, p.idesc,
+                                                  (i | c2 | k) ? 1u : 0u);
+                            }
+                        }
+                        umma_arrive<CL>(ptx::smem_u32(&s_empty[stage]));
+                        if (++stage == stages) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
+                    }
+                    if (!ok) break;
+                    umma_arrive<CL>(ptx::smem_u32(&s_tfull[buf])); // accumulator complete
+                    continue;
+                }
                 for (uint32_t kb = c.kb0; kb < c.kb1; ++kb) {
                     ok = bounded_wait(ptx::smem_u32(&s_full[stage]), phase, &s_abort, p.status,
                                       ST_MMA_WAIT_FULL);
                     if (!ok) break;
                     ptx::tc_fence_after();
-                    const uint32_t sa = ring + stage * STAGE_BYTES;
-                    const uint32_t sb = sa + A_TILE_BYTES;
+                    const uint32_t sa = ring + stage * pitch;
+                    const uint32_t sb = sa + a_bytes;
                     const uint64_t ad = ptx::make_smem_desc(sa, a_lbo, 1024u);
                     const uint64_t bd = ptx::make_smem_desc(sb, b_lbo, 1024u);
 #pragma unroll
@@ -522,7 +644,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         uint32_t       it   = 0, nstore = 0;
         bool           ok   = true;
         for (uint32_t w = unit; ok && w < p.num_work; w += units, ++it) {
-            const WorkCoord c      = decode_work(p, w, BN, BLOCK_M * CL);
+            const WorkCoord c      = decode_work(p, w, BN, tile_m);
             const uint32_t  buf    = it % NUM_ACC;
             const uint32_t  aphase = (it / NUM_ACC) & 1u;
             // A 512-wide tile is drained as two 256-column halves, each published (s_tfull[h])
@@ -546,7 +668,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 // for a fixed column j the warp writes 32 consecutive elements: coalesced stores
                 // straight from registers, no staging.  Used when the caller's small dimension
                 // had to become the MMA's N extent (skinny problems).
-                const uint32_t i = c.m0 + q * 32u + lane;
+                // Rows at and beyond p.bm belong to the next slab (the MMA computed them from
+                // whatever follows the slab in shared memory): never stored.
+                const uint32_t i      = c.m0 + q * 32u + lane;
+                const bool     i_live = (q * 32u + lane) < p.bm && i < p.M;
 #pragma unroll 1
                 for (int ch = 0; ch < (BN + 31) / 32; ++ch) {
                     uint32_t v[32];
@@ -557,7 +682,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                         __syncwarp();
                         if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&s_tempty[buf]));
                     }
-                    if (i < p.M) {
+                    if (i_live) {
                         const size_t base = (static_cast<size_t>(c.z_out) * p.N + c.n0 + ch * 32) * p.M + i;
 #pragma unroll
                         for (int r = 0; r < 32; ++r) {
@@ -661,6 +786,7 @@ __global__ void __launch_bounds__(256)
 {
     const uint64_t total4 = (mn * batch) >> 2; // mn is a multiple of 4
     const uint64_t mn4    = mn >> 2;
+    ptx::grid_dep_wait(); // the partials are complete once the GEMM grid before this one has finished
     for (uint64_t i = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x; i < total4;
          i += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
         const uint64_t z   = i / mn4;

@@ -201,7 +201,7 @@ template <int BN, int OUT>
 static cudaError_t set_smem_attr_narrow_one()
 {
     cudaError_t e = cudaFuncSetAttribute(gemm_umma_kernel<BN, OUT, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)gemm_smem_bytes(BN, 1, max_stages(BN, 1, true), true));
+                                         (int)SLAB_SMEM_LIMIT);
     if (e == cudaSuccess && BN < 64)
         e = cudaFuncSetAttribute(gemm_umma_kernel<BN, OUT, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)gemm_smem_bytes(BN, 1, max_stages(BN, 1, false), false));
@@ -493,6 +493,30 @@ static int encode_operand(CUtensorMap* tm, bool bf16, const void* base, uint32_t
     return encode_map(tm, dt, 2, base, rows, K, batch, 64, BLOCK_K);
 }
 
+// Operand of the transposed (slab) variant, `kc` k-blocks per box.
+//   K-major, K % 64 == 0: 4-D view [batch][K/64][rows][64] (strides: rows K elements apart,
+//     chunks 128 bytes apart), box 64 x box_rows x kc: lands as kc consecutive row-block tiles.
+//   K-major otherwise: the plain 3-D map, one k-block per box (kc == 1).
+//   MN-major: [batch][K][rows], box 64 (MN) x 64 * kc (K).
+static int encode_operand_slab(CUtensorMap* tm, bool bf16, const void* base, uint32_t rows, uint32_t K,
+                               size_t batch, bool mn_major, uint32_t box_rows, uint32_t kc, bool k4d)
+{
+    const CUtensorMapDataType dt = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    if (mn_major) return encode_map(tm, dt, 2, base, rows, K, batch, 64, BLOCK_K * kc);
+    if (!k4d) return encode_map(tm, dt, 2, base, K, rows, batch, BLOCK_K, box_rows);
+    const cuuint64_t dims[4]    = {(cuuint64_t)BLOCK_K, rows, K / BLOCK_K, batch};
+    const cuuint64_t strides[3] = {(cuuint64_t)K * 2, (cuuint64_t)BLOCK_K * 2, (cuuint64_t)rows * K * 2};
+    const cuuint32_t box[4]     = {(cuuint32_t)BLOCK_K, box_rows, kc, 1};
+    const cuuint32_t estr[4]    = {1, 1, 1, 1};
+    const CUresult   r = g_encode(tm, dt, 4, const_cast<void*>(base), dims, strides, box, estr,
+                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(B200_GEMM_ERR_CUDA, "cuTensorMapEncodeTiled (4-D) failed (%d) rows=%u K=%u box_rows=%u kc=%u", (int)r, rows, K,
+                    box_rows, kc);
+    return B200_GEMM_OK;
+}
+
 // ------------------------------------------------------------------------------------------
 // Launch
 // ------------------------------------------------------------------------------------------
@@ -565,6 +589,29 @@ static cudaError_t launch_generic(const Problem& p, cudaStream_t s)
     return cudaGetLastError();
 }
 
+// Split-K reduction pass, launched as a programmatic dependent of the GEMM kernel before it
+// in the stream: its blocks are set up while the GEMM's last tiles drain and start reading the
+// partials (after griddepcontrol.wait) the moment the GEMM grid has completed.
+static cudaError_t launch_reduce(int out, unsigned blocks, cudaStream_t s, const float* ws, void* d, uint64_t mn,
+                                 uint32_t split, uint32_t batch)
+{
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim            = dim3(blocks);
+    lc.blockDim           = dim3(256);
+    lc.dynamicSmemBytes   = 0;
+    lc.stream             = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs                                           = attr;
+    lc.numAttrs                                        = 1;
+    switch (out) {
+        case OUT_F32: return cudaLaunchKernelEx(&lc, splitk_reduce_kernel<OUT_F32>, ws, d, mn, split, batch);
+        case OUT_F16: return cudaLaunchKernelEx(&lc, splitk_reduce_kernel<OUT_F16>, ws, d, mn, split, batch);
+        default: return cudaLaunchKernelEx(&lc, splitk_reduce_kernel<OUT_BF16>, ws, d, mn, split, batch);
+    }
+}
+
 static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_config* user_cfg)
 {
     int st = validate(p);
@@ -618,11 +665,48 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
         cfg.cluster = 1;
         cfg.tile_n  = v.N <= 16 ? 16 : (v.N <= 32 ? 32 : (v.N <= 64 ? 64 : 128));
         if (v.b_mn && cfg.tile_n < 64) cfg.tile_n = 64;
-        cfg.stages = max_stages(cfg.tile_n, 1, transposed);
+    }
+    // Transposed problems are HBM-bound streams of A' (the caller's large operand).  Its rows are
+    // cut into slabs of `bm` <= 128 rows so that the slabs fill whole waves of the SMs: every SM
+    // streams the same number of bytes, no K partition and no reduction pass is needed.  (The
+    // MMA still spans 128 rows; the rows past the slab are never stored.)  An M-major A' is
+    // loaded in 64-row boxes, so its slabs are 64 or 128 rows.
+    uint32_t bm = BLOCK_M;
+    if (transposed && !user_cfg) {
+        const uint32_t sms       = (uint32_t)ctx->sm_count;
+        const uint32_t step      = v.a_mn ? 64u : 8u;
+        uint64_t       best_cost = ~0ull;
+        uint32_t       best_bm = 0, best_tiles = 0;
+        for (uint32_t cand = step; cand <= (uint32_t)BLOCK_M; cand += step) {
+            const uint64_t tiles = (uint64_t)((v.M + cand - 1) / cand) * p.batch;
+            const uint64_t waves = (tiles + sms - 1) / sms;
+            const uint64_t cost  = waves * (cand + 8); // rows streamed per SM + a per-tile overhead
+            if (cost <= best_cost) {
+                best_cost  = cost;
+                best_bm    = cand;
+                best_tiles = (uint32_t)std::min<uint64_t>(tiles, 0xffffffffu);
+            }
+        }
+        if (best_tiles * 10u >= sms * 8u) { // enough slabs to occupy the chip without splitting K
+            bm          = best_bm;
+            cfg.split_k = 1;
+        }
     }
     uint32_t kb_per_split = 0;
     legalize(cfg, v, &kb_per_split);
-    if (narrow) cfg.stages = max_stages(cfg.tile_n, 1, transposed);
+    // Transposed variant: a ring slot holds kc k-blocks.  K-major operands fetch them with one
+    // 4-D box over a [chunk][row][64] view of the matrix, which needs K to be a multiple of 64.
+    uint32_t   kc  = 1;
+    const bool k4d = transposed && v.K % BLOCK_K == 0;
+    if (transposed && (k4d || (v.a_mn && v.b_mn))) {
+        kc = kb_per_split >= 16 ? 4u : (kb_per_split >= 4 ? 2u : 1u);
+        if (cfg.split_k > 1 && kb_per_split % kc) { // partitions start on slot boundaries
+            const uint32_t k_blocks = (v.K + BLOCK_K - 1) / BLOCK_K;
+            kb_per_split            = (kb_per_split + kc - 1) / kc * kc;
+            cfg.split_k             = (int)((k_blocks + kb_per_split - 1) / kb_per_split);
+        }
+    }
+    if (narrow) cfg.stages = transposed ? slab_max_stages((int)bm, cfg.tile_n, (int)kc) : max_stages(cfg.tile_n, 1, false);
 
     if (!user_cfg && cfg.split_k > 1 && !transposed && v.N % 4) { // the table's nearest entry may not fit
         cfg.split_k = 1;
@@ -639,7 +723,10 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     gp.K            = v.K;
     gp.batch        = (uint32_t)p.batch;
     const uint32_t cl   = (uint32_t)cfg.cluster;
-    gp.m_tiles      = (v.M + BLOCK_M * cl - 1) / (BLOCK_M * cl);
+    gp.bm           = bm;
+    gp.kc           = kc;
+    gp.k4d          = k4d ? 1u : 0u;
+    gp.m_tiles      = transposed ? (v.M + bm - 1) / bm : (v.M + BLOCK_M * cl - 1) / (BLOCK_M * cl);
     gp.n_tiles      = (v.N + bn - 1) / bn;
     gp.k_blocks     = (v.K + BLOCK_K - 1) / BLOCK_K;
     gp.split_k      = split;
@@ -669,7 +756,8 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     }
     // Streaming (HBM-bound) views rotate the K order per work unit; see the producer.
     const bool streaming = narrow || std::min(v.M, v.N) <= 256;
-    gp.k_skew = streaming ? std::max<uint32_t>(1u, kb_per_split / std::max<uint32_t>(1u, std::min<uint32_t>((uint32_t)work, (uint32_t)ctx->sm_count))) : 0u;
+    const uint32_t slots_per_unit = (kb_per_split + kc - 1) / kc; // K steps of one work unit
+    gp.k_skew = streaming ? std::max<uint32_t>(1u, slots_per_unit / std::max<uint32_t>(1u, std::min<uint32_t>((uint32_t)work, (uint32_t)ctx->sm_count))) : 0u;
 
     // Split-K partials go to this stream's cached f32 workspace, laid out [batch][split][Mk][Nk].
     float*       ws       = nullptr;
@@ -691,8 +779,13 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     }
 
     CUtensorMap tmA, tmB, tmD;
-    st = encode_operand(&tmA, bf16, v.a, v.M, v.K, p.batch, v.a_mn, BLOCK_M);
-    if (st == B200_GEMM_OK) st = encode_operand(&tmB, bf16, v.b, v.N, v.K, p.batch, v.b_mn, (uint32_t)umma_n / cl);
+    if (transposed) {
+        st = encode_operand_slab(&tmA, bf16, v.a, v.M, v.K, p.batch, v.a_mn, bm, kc, k4d);
+        if (st == B200_GEMM_OK) st = encode_operand_slab(&tmB, bf16, v.b, v.N, v.K, p.batch, v.b_mn, (uint32_t)bn, kc, k4d);
+    } else {
+        st = encode_operand(&tmA, bf16, v.a, v.M, v.K, p.batch, v.a_mn, BLOCK_M);
+        if (st == B200_GEMM_OK) st = encode_operand(&tmB, bf16, v.b, v.N, v.K, p.batch, v.b_mn, (uint32_t)umma_n / cl);
+    }
     if (st == B200_GEMM_OK && transposed) {
         tmD    = tmA; // not used by the transposed epilogue; any valid descriptor will do
         gp.out = split > 1 ? static_cast<void*>(ws) : v.d;
@@ -710,7 +803,7 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
         return st;
     }
 
-    const uint32_t smem     = gemm_smem_bytes(bn, (int)cl, cfg.stages, transposed);
+    const uint32_t smem     = transposed ? slab_smem_bytes((int)bm, bn, (int)kc, cfg.stages) : gemm_smem_bytes(bn, (int)cl, cfg.stages);
     const uint32_t units    = std::min<uint32_t>(gp.num_work, (uint32_t)ctx->sm_count / cl);
     const int      kern_out = split > 1 ? OUT_F32 : out;
     cudaError_t    e;
@@ -745,13 +838,8 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
         const uint64_t mn     = (uint64_t)v.M * v.N;
         const uint64_t total4 = mn * p.batch / 4;
         const unsigned blocks = (unsigned)std::min<uint64_t>((total4 + 255) / 256, (uint64_t)ctx->sm_count * 8);
-        switch (out) {
-            case OUT_F32: splitk_reduce_kernel<OUT_F32><<<blocks, 256, 0, stream>>>(ws, v.d, mn, split, (uint32_t)p.batch); break;
-            case OUT_F16: splitk_reduce_kernel<OUT_F16><<<blocks, 256, 0, stream>>>(ws, v.d, mn, split, (uint32_t)p.batch); break;
-            default: splitk_reduce_kernel<OUT_BF16><<<blocks, 256, 0, stream>>>(ws, v.d, mn, split, (uint32_t)p.batch); break;
-        }
+        e = launch_reduce(out, blocks, stream, ws, v.d, mn, split, (uint32_t)p.batch);
         g_launches.fetch_add(1, std::memory_order_relaxed);
-        e = cudaGetLastError();
         if (ws_stream_ordered) cudaFreeAsync(ws, stream);
         if (e != cudaSuccess) return fail(B200_GEMM_ERR_CUDA, "split-K reduce launch failed: %s", cudaGetErrorString(e));
     }
@@ -880,6 +968,9 @@ static int run_gemm_static(const Problem& p, cudaStream_t stream, const b200_gem
     gp.N            = v.N;
     gp.K            = v.K;
     gp.batch        = (uint32_t)p.batch;
+    gp.bm           = BLOCK_M;
+    gp.kc           = 1;
+    gp.k4d          = 0;
     gp.m_tiles      = (v.M + BLOCK_M * cl - 1) / (BLOCK_M * cl);
     gp.n_tiles      = (v.N + bn - 1) / bn;
     gp.k_blocks     = (v.K + BLOCK_K - 1) / BLOCK_K;

@@ -52,9 +52,9 @@ struct GemmParams {
     void*    out;          // transposed epilogue only: base of the (Nk x Mk, row-major) output
     uint32_t k_skew;       // work unit w starts its K loop (w * k_skew) k-blocks in (0 = in order)
     uint32_t stagger;      // 512-wide tiles: k-blocks by which the two column halves are staggered
-    uint32_t bm;           // transposed epilogue only: rows of A' per tile ("slab" height, 8 .. 128)
-    uint32_t kc;           // transposed epilogue only: k-blocks per ring slot (1, 2 or 4)
-    uint32_t k4d;          // transposed epilogue only: K-major operands use the 4-D (chunked K) maps
+    uint32_t bm;           // one-CTA kernels: rows of A' per tile (128; 8 .. 128 with the transposed epilogue)
+    uint32_t kc;           // one-CTA kernels: k-blocks per ring slot (1, 2 or 4)
+    uint32_t k4d;          // one-CTA kernels: K-major operands use the 4-D (chunked K) maps
 };
 
 constexpr int      BLOCK_M        = 128;
@@ -104,6 +104,17 @@ __host__ __device__ constexpr int slab_max_stages(int bm, int bn, int kc)
 {
     int s = static_cast<int>((SLAB_SMEM_LIMIT - 1024u - slab_slack_bytes(kc)) / slab_stage_bytes(bm, bn, kc));
     return s > MAX_SLAB_STAGES ? MAX_SLAB_STAGES : s;
+}
+
+// One-CTA kernels with the staged epilogue and kc k-blocks per slot.
+__host__ __device__ constexpr uint32_t slot_smem_bytes(int bn, int kc, int stages)
+{
+    return static_cast<uint32_t>(stages) * kc * stage_bytes(bn, 1) + EPI_BYTES + 1024;
+}
+__host__ __device__ constexpr int slot_max_stages(int bn, int kc)
+{
+    int s = static_cast<int>((232448u - 512u - EPI_BYTES - 1024u) / (kc * stage_bytes(bn, 1)));
+    return s > MAX_STAGES ? MAX_STAGES : s;
 }
 
 // Deepest ring that fits the 227 KiB a CTA may use (static barriers included).
@@ -327,11 +338,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 
     // Bytes of A' per ring slot and slot pitch: compile-time for the staged epilogue; the
     // transposed variant stages p.bm (a multiple of 8, <= 128) rows of A' per slot.
-    // A slot of the transposed variant holds kc k-blocks: [A' k-block 0 .. kc-1][B' k-block 0 .. kc-1].
-    const uint32_t kc      = TR ? p.kc : 1u;
-    const uint32_t a_bytes = TR ? p.bm * (BLOCK_K * 2u) : A_TILE_BYTES;
-    const uint32_t pitch   = TR ? kc * (a_bytes + B_TILE_BYTES) : STAGE_BYTES;
-    const uint32_t tile_m  = TR ? p.bm : static_cast<uint32_t>(BLOCK_M * CL);
+    // One-CTA kernels up to 256 columns use "slots" of kc k-blocks:
+    // [A' k-block 0 .. kc-1][B' k-block 0 .. kc-1], each operand fetched by one TMA instruction
+    // (the per-slot barrier and issue work of the two single-thread roles is amortised over kc
+    // k-blocks; with narrow tiles that work, not the tensor pipe, bounds the K loop).  A' has
+    // p.bm rows per k-block: 128, or a shorter slab with the transposed epilogue.
+    constexpr bool SLOT    = (CL == 1) && (NSUB == 1);
+    const uint32_t kc      = SLOT ? p.kc : 1u;
+    const uint32_t a_bytes = SLOT ? p.bm * (BLOCK_K * 2u) : A_TILE_BYTES;
+    const uint32_t pitch   = SLOT ? kc * (a_bytes + B_TILE_BYTES) : STAGE_BYTES;
+    const uint32_t tile_m  = SLOT ? p.bm : static_cast<uint32_t>(BLOCK_M * CL);
 
     const uint32_t ring = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u; // ring of operand tiles
     const uint32_t epi  = ring + stages * pitch;                      // epilogue staging (unused when TR)
@@ -380,8 +396,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 // are a power of two apart, and same-offset reads from thousands of rows land on
                 // a few memory channels.
                 const uint32_t nkb = c.kb1 - c.kb0;
-                if constexpr (TR) {
-                    // Slab variant: one slot = kc k-blocks of A' (p.bm rows) and of B' (BN rows),
+                if constexpr (SLOT) {
+                    // One slot = kc k-blocks of A' (p.bm rows) and of B' (BN rows),
                     // one TMA instruction per operand (per 64-row half for an MN-major operand).
                     // Boxes that reach past K read zeros, so a ragged last slot needs no care.
                     const uint32_t nst  = (nkb + kc - 1u) / kc;
@@ -568,7 +584,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                 if (!ok) break;
                 ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * ACC_COLS;
-                if constexpr (TR) {
+                if constexpr (SLOT) {
                     // kc k-blocks per slot; see the producer for the slot layout.
                     const uint32_t nst    = (c.kb1 - c.kb0 + kc - 1u) / kc;
                     const uint32_t half   = kc * (64u * BLOCK_K * 2u);

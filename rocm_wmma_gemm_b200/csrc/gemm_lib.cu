@@ -493,7 +493,7 @@ static int encode_operand(CUtensorMap* tm, bool bf16, const void* base, uint32_t
     return encode_map(tm, dt, 2, base, rows, K, batch, 64, BLOCK_K);
 }
 
-// Operand of the transposed (slab) variant, `kc` k-blocks per box.
+// Operand of a one-CTA kernel, `kc` k-blocks per box.
 //   K-major, K % 64 == 0: 4-D view [batch][K/64][rows][64] (strides: rows K elements apart,
 //     chunks 128 bytes apart), box 64 x box_rows x kc: lands as kc consecutive row-block tiles.
 //   K-major otherwise: the plain 3-D map, one k-block per box (kc == 1).
@@ -694,24 +694,33 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     }
     uint32_t kb_per_split = 0;
     legalize(cfg, v, &kb_per_split);
-    // Transposed variant: a ring slot holds kc k-blocks.  K-major operands fetch them with one
-    // 4-D box over a [chunk][row][64] view of the matrix, which needs K to be a multiple of 64.
-    uint32_t   kc  = 1;
-    const bool k4d = transposed && v.K % BLOCK_K == 0;
-    if (transposed && (k4d || (v.a_mn && v.b_mn))) {
-        kc = kb_per_split >= 16 ? 4u : (kb_per_split >= 4 ? 2u : 1u);
+    if (!user_cfg && cfg.split_k > 1 && !transposed && v.N % 4) { // the table's nearest entry may not fit
+        cfg.split_k = 1;
+        legalize(cfg, v, &kb_per_split);
+    }
+    // One-CTA kernels up to 256 columns: a ring slot holds kc k-blocks (see the kernel).  The
+    // narrower the tile, the less tensor-pipe time one k-block is worth against the fixed
+    // per-slot work of the producer and MMA threads, so narrow tiles take more k-blocks per
+    // slot; at least three slots must fit.  K-major operands fetch a slot with one 4-D box over
+    // a [chunk][row][64] view of the matrix, which needs K to be a multiple of 64.
+    const bool slot = cfg.cluster == 1 && cfg.tile_n <= 256;
+    uint32_t   kc   = 1;
+    const bool k4d  = slot && v.K % BLOCK_K == 0;
+    if (slot && (k4d || (v.a_mn && v.b_mn))) {
+        kc = cfg.tile_n >= 256 ? 1u : (cfg.tile_n >= 128 ? 2u : 4u);
+        auto slots_fit = [&](uint32_t c) {
+            return transposed ? slab_max_stages((int)bm, cfg.tile_n, (int)c) : slot_max_stages(cfg.tile_n, (int)c);
+        };
+        while (kc > 1 && (kb_per_split < 2 * kc || slots_fit(kc) < 3)) kc /= 2;
         if (cfg.split_k > 1 && kb_per_split % kc) { // partitions start on slot boundaries
             const uint32_t k_blocks = (v.K + BLOCK_K - 1) / BLOCK_K;
             kb_per_split            = (kb_per_split + kc - 1) / kc * kc;
             cfg.split_k             = (int)((k_blocks + kb_per_split - 1) / kb_per_split);
         }
     }
-    if (narrow) cfg.stages = transposed ? slab_max_stages((int)bm, cfg.tile_n, (int)kc) : max_stages(cfg.tile_n, 1, false);
+    if (transposed) cfg.stages = slab_max_stages((int)bm, cfg.tile_n, (int)kc);
+    else if (slot && (narrow || kc > 1)) cfg.stages = slot_max_stages(cfg.tile_n, (int)kc);
 
-    if (!user_cfg && cfg.split_k > 1 && !transposed && v.N % 4) { // the table's nearest entry may not fit
-        cfg.split_k = 1;
-        legalize(cfg, v, &kb_per_split);
-    }
     const int      bn   = cfg.tile_n;
     const int      out  = out_kind(p.types);
     const bool     bf16 = in_is_bf16(p.types);
@@ -779,7 +788,7 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     }
 
     CUtensorMap tmA, tmB, tmD;
-    if (transposed) {
+    if (slot) {
         st = encode_operand_slab(&tmA, bf16, v.a, v.M, v.K, p.batch, v.a_mn, bm, kc, k4d);
         if (st == B200_GEMM_OK) st = encode_operand_slab(&tmB, bf16, v.b, v.N, v.K, p.batch, v.b_mn, (uint32_t)bn, kc, k4d);
     } else {
@@ -803,7 +812,8 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
         return st;
     }
 
-    const uint32_t smem     = transposed ? slab_smem_bytes((int)bm, bn, (int)kc, cfg.stages) : gemm_smem_bytes(bn, (int)cl, cfg.stages);
+    const uint32_t smem     = transposed ? slab_smem_bytes((int)bm, bn, (int)kc, cfg.stages)
+                              : (slot ? slot_smem_bytes(bn, (int)kc, cfg.stages) : gemm_smem_bytes(bn, (int)cl, cfg.stages));
     const uint32_t units    = std::min<uint32_t>(gp.num_work, (uint32_t)ctx->sm_count / cl);
     const int      kern_out = split > 1 ? OUT_F32 : out;
     cudaError_t    e;

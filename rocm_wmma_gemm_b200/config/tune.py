@@ -43,7 +43,7 @@ PARAMS = ["tile_m", "tile_n", "stages", "split_k", "raster"]
 SPACE = {
     "tile_m": [128, 256],
     "tile_n": [64, 128, 256, 512],
-    "stages": [2, 3, 4, 5, 6, 8],
+    "stages": [2, 3, 4, 6, 8, 12],
     "split_k": [1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 12, 14, 16, 24, 32],
     "raster": [0, 1, 2, 4, 8, 16, 32],
 }
@@ -75,7 +75,7 @@ def stage_bytes(tile_n: int, cluster: int) -> int:
 
 
 def max_stages(tile_n: int, cluster: int) -> int:
-    return min(8, (SMEM_LIMIT - 512 - EPILOGUE_BYTES - 1024) // stage_bytes(tile_n, cluster))
+    return min(12, (SMEM_LIMIT - 512 - EPILOGUE_BYTES - 1024) // stage_bytes(tile_n, cluster))
 
 
 def check_constraints(cfg, M=None, N=None, K=None, lc=0) -> bool:
@@ -163,11 +163,33 @@ class InProcessEvaluator:
         cfg = self.g.GemmConfig(d["tile_m"], d["tile_n"], d["stages"], d["cluster"], d["split_k"], d["raster"])
         try:
             t1 = self._batch(M, N, K, la, lb, lc, cfg, self.warmup)
+            if t1 < 0.25:
+                return self._graph(M, N, K, la, lb, lc, cfg, t1)
             # long kernels need fewer repetitions for a stable number: ~4 ms per timed batch
             iters = max(1, min(self.iters, int(4.0 / max(t1, 1e-3))))
             return statistics.median(self._batch(M, N, K, la, lb, lc, cfg, iters) for _ in range(self.reps))
         except self.g.GemmError:
             return INF
+
+    def _graph(self, M, N, K, la, lb, lc, cfg, t1):
+        """Short kernels: a call costs the host more than the device, so the calls are replayed
+        from a CUDA graph and the device time alone is compared."""
+        torch = self.torch
+        n = max(5, min(50, int(2.0 / max(t1, 1e-3))))
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(n):
+                self.loader.gemm(self.C, self.A, self.B, M, N, K, lc, la, lb, types=self.types, config=cfg)
+        graph.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(self.reps):
+            self.e0.record()
+            graph.replay()
+            self.e1.record()
+            torch.cuda.synchronize()
+            times.append(self.e0.elapsed_time(self.e1) / n)
+        return statistics.median(times)
 
 
 class SubprocessEvaluator:
@@ -223,7 +245,12 @@ def refine(evaluate, shape, layout, candidates, rounds=3):
         for c in candidates:
             times[c].append(evaluate(*shape, *layout, c))
     med = {c: statistics.median(t) for c, t in times.items()}
-    best = min(med, key=med.get)
+    fastest = min(med.values())
+    # Under the power cap two good configurations differ by less than the clocks move: among
+    # those within 2 % of the fastest prefer the one that moves fewer bytes per FLOP (larger
+    # tile, fewer K partitions), then the measured time.
+    near = [c for c in med if med[c] <= fastest * 1.02]
+    best = min(near, key=lambda c: (-(c[0] * c[1]), c[3], med[c]))
     return best, med[best]
 
 
@@ -241,6 +268,29 @@ def tune_layout(evaluate, shape, layout, budget, seeds, rng, log):
         return None
     best, t = refine(evaluate, shape, layout, finalists)
     return {"config": best, "time_ms": t, "evaluations": res.evaluations}
+
+
+def consolidate(evaluate, table, shape, out):
+    """Cross-layout check of one size: every layout re-times the winners of all layouts of the
+    size, interleaved, and keeps the fastest.  A search that stalled in a poor niche for one
+    layout (or was timed while the clocks were low) is repaired by its neighbours' results."""
+    entries = table.get(shape, {})
+    candidates = sorted({from_dict(e["config"]) for e in entries.values()})
+    if len(candidates) < 2:
+        return
+    M, N, K = shape
+    for layout, e in entries.items():
+        valid = [c for c in candidates if check_constraints(c, M, N, K, layout[2])]
+        if len(valid) < 2:
+            continue
+        best, t = refine(evaluate, shape, layout, valid, rounds=5)
+        if best != from_dict(e["config"]):
+            print(f"{M}x{N}x{K} A={'rc'[layout[0]]} B={'rc'[layout[1]]} C={'rc'[layout[2]]}: consolidated "
+                  f"{e['config']} ({e['time_ms']:.4f} ms) -> {to_dict(best)} ({t:.4f} ms)", flush=True)
+        e["config"] = to_dict(best)
+        e["time_ms"] = round(t, 5)
+        e["tflops"] = round(2.0 * M * N * K / (t * 1e-3) / 1e12, 1)
+    save_table(out, table)
 
 
 def main(argv=None):
@@ -301,6 +351,7 @@ def main(argv=None):
             save_table(out, table)  # resume point
             print(f"{M}x{N}x{K} A={'rc'[layout[0]]} B={'rc'[layout[1]]} C={'rc'[layout[2]]}: {to_dict(r['config'])} "
                   f"{r['time_ms']:.4f} ms {tflops:.0f} TFLOP/s ({r['evaluations']} evals)", flush=True)
+        consolidate(evaluate, table, shape, out)
     print("saved", out)
     return 0
 

@@ -379,8 +379,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     }
     ptx::tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
-    // Split-K: let the reduction pass be scheduled now; it waits for this grid to complete.
-    if (p.split_k > 1u) ptx::grid_dep_launch();
+    // Programmatic dependent launch, both directions.  This grid may have been scheduled while
+    // the kernel before it in the stream was still draining: everything above touched only this
+    // CTA's shared memory and TMEM; global memory is first used below, after the wait.  And the
+    // kernel after this one (the split-K reduction, or the next GEMM) may be scheduled as SMs
+    // free up; it waits for this grid to complete before it reads or writes anything.
+    ptx::grid_dep_wait();
+    ptx::grid_dep_launch();
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -803,6 +808,7 @@ __global__ void __launch_bounds__(256)
     const uint64_t total4 = (mn * batch) >> 2; // mn is a multiple of 4
     const uint64_t mn4    = mn >> 2;
     ptx::grid_dep_wait(); // the partials are complete once the GEMM grid before this one has finished
+    ptx::grid_dep_launch();
     for (uint64_t i = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x; i < total4;
          i += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
         const uint64_t z   = i / mn4;

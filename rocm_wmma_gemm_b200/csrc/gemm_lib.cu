@@ -127,14 +127,16 @@ static int search_closest(size_t m, size_t n, size_t k, int tg, int la, int lb, 
 // Selection order of the reference's find_best_config
 // (rocm_wmma_gemm/config/generate_config.py:238-271): exact in the requested type group,
 // exact in group 0, closest in the requested group, closest in group 0, default.
-static int find_best_config(size_t m, size_t n, size_t k, int tg, int la, int lb, int lc)
+static int find_best_config(size_t m, size_t n, size_t k, int tg, int la, int lb, int lc, bool* exact = nullptr)
 {
+    if (exact) *exact = true;
     int r = search_exact(m, n, k, tg, la, lb, lc);
     if (r >= 0) return r;
     if (tg != 0) {
         r = search_exact(m, n, k, 0, la, lb, lc);
         if (r >= 0) return r;
     }
+    if (exact) *exact = false;
     r = search_closest(m, n, k, tg, la, lb, lc);
     if (r < 0 && tg != 0) r = search_closest(m, n, k, 0, la, lb, lc);
     if (r < 0) r = k_default_config;
@@ -448,8 +450,9 @@ static bool env_config(b200_gemm_config* out)
     return true;
 }
 
-static b200_gemm_config resolve_config(const Problem& p, const b200_gemm_config* user, int* idx)
+static b200_gemm_config resolve_config(const Problem& p, const b200_gemm_config* user, int* idx, bool* tuned = nullptr)
 {
+    if (tuned) *tuned = true; // explicit configurations are taken as they are
     if (user) {
         if (idx) *idx = -1;
         return *user;
@@ -459,9 +462,36 @@ static b200_gemm_config resolve_config(const Problem& p, const b200_gemm_config*
         if (idx) *idx = -1;
         return forced;
     }
-    const int i = find_best_config(p.M, p.N, p.K, out_is_f32(p.types) ? 1 : 0, p.la, p.lb, p.lc);
+    const int i = find_best_config(p.M, p.N, p.K, out_is_f32(p.types) ? 1 : 0, p.la, p.lb, p.lc, tuned);
     if (idx) *idx = i;
     return k_configs[i];
+}
+
+// A configuration borrowed from the nearest tuned size can cut a smaller problem into far fewer
+// work units than the chip has SMs.  Step down the tile ladder, then partition K, until at
+// least half of the SMs have a CTA.  Sizes with an entry of their own are never touched.
+static void adapt_config(b200_gemm_config& c, const View& v, size_t batch, int sms)
+{
+    static const int ladder[5][3] = {{256, 512, 2}, {256, 256, 2}, {128, 256, 1}, {128, 128, 1}, {128, 64, 1}};
+    auto ctas = [&](int tm, int tn, int cl) {
+        return (uint64_t)((v.M + tm - 1) / tm) * ((v.N + tn - 1) / tn) * batch * (uint64_t)cl;
+    };
+    const uint64_t want = (uint64_t)sms / 2;
+    if (c.split_k != 1 || ctas(c.tile_m, c.tile_n, c.cluster) * (uint64_t)c.split_k >= want) return;
+    int at = 0;
+    while (at < 4 && ladder[at][0] * ladder[at][1] > c.tile_m * c.tile_n) ++at;
+    while (at < 4 && ctas(ladder[at][0], ladder[at][1], ladder[at][2]) < want) ++at;
+    c.tile_m  = ladder[at][0];
+    c.tile_n  = ladder[at][1];
+    c.cluster = ladder[at][2];
+    c.stages  = MAX_STAGES;
+    c.raster  = 0;
+    const uint64_t n        = ctas(c.tile_m, c.tile_n, c.cluster);
+    const uint32_t k_blocks = (v.K + BLOCK_K - 1) / BLOCK_K;
+    if (n < want && k_blocks >= 8 && v.N % 4 == 0) {
+        const uint64_t by_work = ((uint64_t)sms * 8 / 10 + n - 1) / n;
+        c.split_k              = (int)std::max<uint64_t>(1, std::min<uint64_t>({by_work, (uint64_t)k_blocks / 4, (uint64_t)64}));
+    }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -555,13 +585,16 @@ static cudaError_t launch_bn(int out, uint32_t units_wanted, int* pair_units, ui
     lc.blockDim           = dim3(GEMM_THREADS);
     lc.dynamicSmemBytes   = smem;
     lc.stream             = s;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id               = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = CL;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
-    lc.attrs                 = attr;
-    lc.numAttrs              = 1;
+    // The kernel's set-up may overlap the tail of the kernel before it (see the kernel).
+    attr[1].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs                                           = attr;
+    lc.numAttrs                                        = 2;
     switch (out) {
         case OUT_F32: return cudaLaunchKernelEx(&lc, gemm_umma_kernel<BN, OUT_F32, CL, TR>, a, b, d, gp);
         case OUT_F16: return cudaLaunchKernelEx(&lc, gemm_umma_kernel<BN, OUT_F16, CL, TR>, a, b, d, gp);
@@ -653,9 +686,11 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
         return B200_GEMM_OK;
     }
 
-    b200_gemm_config cfg = resolve_config(p, user_cfg, nullptr);
-    st                   = check_config(cfg);
+    bool             tuned = true;
+    b200_gemm_config cfg   = resolve_config(p, user_cfg, nullptr, &tuned);
+    st                     = check_config(cfg);
     if (st != B200_GEMM_OK) return st;
+    if (!tuned) adapt_config(cfg, v, p.batch, ctx->sm_count);
     // Narrow kernel views (at most 64 columns) run on the narrow one-CTA variants whatever
     // tile the table names: tile_n is the smallest compiled width that covers N (an MN-major
     // B' is loaded in 64-row boxes, so it needs 64) and the ring is as deep as fits.

@@ -467,31 +467,58 @@ static b200_gemm_config resolve_config(const Problem& p, const b200_gemm_config*
     return k_configs[i];
 }
 
-// A configuration borrowed from the nearest tuned size can cut a smaller problem into far fewer
-// work units than the chip has SMs.  Step down the tile ladder, then partition K, until at
-// least half of the SMs have a CTA.  Sizes with an entry of their own are never touched.
+// Sizes without a table entry of their own: the entry borrowed from the nearest tuned size is
+// checked against a small cost model of the compiled tile shapes and replaced when the model
+// finds something at least 15 % faster (a 1536^3 problem should not inherit the K partitions
+// of a skinny neighbour, a 512 x 512 x 4096 one not a tile that leaves 140 SMs idle).
+//   time = waves x k-blocks x cycles per k-block + exposed epilogue + launch (+ reduction pass)
+// with cycles per k-block the larger of the tensor-pipe time and the per-slot issue work of the
+// producer / MMA threads, measured on this design.  Sizes with an entry are never touched.
 static void adapt_config(b200_gemm_config& c, const View& v, size_t batch, int sms)
 {
-    static const int ladder[5][3] = {{256, 512, 2}, {256, 256, 2}, {128, 256, 1}, {128, 128, 1}, {128, 64, 1}};
-    auto ctas = [&](int tm, int tn, int cl) {
-        return (uint64_t)((v.M + tm - 1) / tm) * ((v.N + tn - 1) / tn) * batch * (uint64_t)cl;
+    struct Shape {
+        int    tm, tn, cl;
+        double cyc_per_kb, epilogue;
     };
-    const uint64_t want = (uint64_t)sms / 2;
-    if (c.split_k != 1 || ctas(c.tile_m, c.tile_n, c.cluster) * (uint64_t)c.split_k >= want) return;
-    int at = 0;
-    while (at < 4 && ladder[at][0] * ladder[at][1] > c.tile_m * c.tile_n) ++at;
-    while (at < 4 && ctas(ladder[at][0], ladder[at][1], ladder[at][2]) < want) ++at;
-    c.tile_m  = ladder[at][0];
-    c.tile_n  = ladder[at][1];
-    c.cluster = ladder[at][2];
-    c.stages  = MAX_STAGES;
-    c.raster  = 0;
-    const uint64_t n        = ctas(c.tile_m, c.tile_n, c.cluster);
+    static const Shape ladder[5] = {{256, 512, 2, 1060, 5500},
+                                    {256, 256, 2, 540, 2700},
+                                    {128, 256, 1, 570, 2700},
+                                    {128, 128, 1, 500, 1400},
+                                    {128, 64, 1, 400, 800}};
     const uint32_t k_blocks = (v.K + BLOCK_K - 1) / BLOCK_K;
-    if (n < want && k_blocks >= 8 && v.N % 4 == 0) {
-        const uint64_t by_work = ((uint64_t)sms * 8 / 10 + n - 1) / n;
-        c.split_k              = (int)std::max<uint64_t>(1, std::min<uint64_t>({by_work, (uint64_t)k_blocks / 4, (uint64_t)64}));
+    auto model = [&](const Shape& t, int split) {
+        const uint64_t tiles = (uint64_t)((v.M + t.tm - 1) / t.tm) * ((v.N + t.tn - 1) / t.tn) * batch * (uint64_t)split;
+        const uint64_t slots = (uint64_t)(sms / t.cl);
+        const uint64_t waves = (tiles + slots - 1) / slots;
+        const double   kb    = (double)((k_blocks + split - 1) / split);
+        double         cyc   = (double)waves * kb * t.cyc_per_kb + t.epilogue + 3000.0;
+        if (split > 1) cyc += 3000.0 + (double)v.M * v.N * batch * 4.0 * (split + 1) / 4000.0; // partials: ~4 KB per cycle
+        return cyc;
+    };
+    double current = -1.0;
+    for (const Shape& t : ladder)
+        if (t.tm == c.tile_m && t.tn == c.tile_n) current = model(t, c.split_k);
+    double       best = 1e300;
+    const Shape* bt   = nullptr;
+    int          bs   = 1;
+    for (const Shape& t : ladder) {
+        for (int split : {1, 2, 4, 8, 16}) {
+            if (split > 1 && (v.N % 4 != 0 || (uint32_t)split * 4 > k_blocks)) continue;
+            const double m = model(t, split);
+            if (m < best) {
+                best = m;
+                bt   = &t;
+                bs   = split;
+            }
+        }
     }
+    if (!bt || (current > 0 && best > current * 0.85)) return;
+    c.tile_m  = bt->tm;
+    c.tile_n  = bt->tn;
+    c.cluster = bt->cl;
+    c.split_k = bs;
+    c.stages  = MAX_STAGES;
+    c.raster  = ((v.M + bt->tm - 1) / bt->tm) >= 16 ? 8 : 0;
 }
 
 // ------------------------------------------------------------------------------------------

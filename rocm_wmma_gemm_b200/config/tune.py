@@ -140,10 +140,13 @@ class InProcessEvaluator:
         torch = self.torch
         in_dt = torch.bfloat16 if self.types >= 2 else torch.float16
         out_dt = torch.float32 if self.types in (1, 3) else in_dt
-        # the reference tuner's five-value cyclic fill (config/tuner.cpp:107-122)
-        vals = torch.tensor([0.1, 0.125, 0.15, 0.175, 0.2], device="cuda")
-        self.A = vals[torch.arange(M * K, device="cuda") % 5].to(in_dt)
-        self.B = vals[torch.arange(K * N, device="cuda") % 5].to(in_dt)
+        # Seeded normal(0, 1) inputs, not the reference tuner's five-value cyclic fill
+        # (config/tuner.cpp:107-122): B200 runs large GEMMs at its power cap, the clock it
+        # settles at depends on how many operand bits toggle, and with the low-entropy fill the
+        # tuner preferred tiles (256x256) that lose to 256x512 by 10-20 % on random data.
+        gen = torch.Generator(device="cuda").manual_seed(1234)
+        self.A = torch.randn(M * K, device="cuda", generator=gen).to(in_dt)
+        self.B = torch.randn(K * N, device="cuda", generator=gen).to(in_dt)
         self.C = torch.empty(M * N, device="cuda", dtype=out_dt)
         self.shape = (M, N, K)
         self.e0 = torch.cuda.Event(enable_timing=True)
@@ -246,10 +249,11 @@ def refine(evaluate, shape, layout, candidates, rounds=3):
             times[c].append(evaluate(*shape, *layout, c))
     med = {c: statistics.median(t) for c, t in times.items()}
     fastest = min(med.values())
-    # Under the power cap two good configurations differ by less than the clocks move: among
-    # those within 2 % of the fastest prefer the one that moves fewer bytes per FLOP (larger
-    # tile, fewer K partitions), then the measured time.
-    near = [c for c in med if med[c] <= fastest * 1.02]
+    # Under the power cap two good configurations differ by less than the clocks move (a tuning
+    # run is sustained load: every large GEMM settles near the same power-limited rate, while in
+    # short bursts the larger tile is 5 % faster): among those within 4 % of the fastest prefer
+    # the one that moves fewer bytes per FLOP (larger tile, fewer K partitions), then the time.
+    near = [c for c in med if med[c] <= fastest * 1.04]
     best = min(near, key=lambda c: (-(c[0] * c[1]), c[3], med[c]))
     return best, med[best]
 

@@ -60,6 +60,7 @@ DEFAULT_SIZES = [
     (4096, 4096, 2048), (8192, 28672, 8192), (8192, 8192, 28672),
     (16, 8192, 8192), (64, 8192, 8192), (128, 8192, 8192), (16, 28672, 8192), (64, 28672, 8192), (128, 28672, 8192),
     (16384, 16384, 16384), (16384, 8192, 16384), (16384, 4096, 16384), (16384, 2048, 16384),
+    (32768, 32768, 8192), (32768, 16384, 8192), (32768, 8192, 8192), (32768, 4096, 8192),
 ]
 ALL_LAYOUTS = [(0, 0, 0), (0, 1, 0), (1, 0, 0), (1, 1, 0), (0, 0, 1), (0, 1, 1), (1, 0, 1), (1, 1, 1)]  # row-major C first
 LAYOUT_NAME = {0: "row_major", 1: "col_major"}

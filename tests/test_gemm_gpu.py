@@ -354,3 +354,87 @@ def test_concurrent_streams_and_threads():
     for i in range(4):
         for out in results[i]:
             check_parity(3, out, ref, K, SIGMA_UNIFORM, M, N, 0)
+
+
+SLAB_EDGES = [(16, 8200, 576), (33, 9000, 264), (64, 8192 + 56, 320), (8, 20000, 192), (16, 8192, 4096 + 64)]
+
+
+@pytest.mark.parametrize("M,N,K", SLAB_EDGES)
+def test_row_slab_edges(M, N, K):
+    """Skinny problems wide enough for the row-slab partition (147+ slabs of 8..128 rows of the
+    large operand): ragged last slab, K not a multiple of 64 (one k-block per ring slot, plain
+    3-D maps) and long K (four k-blocks per slot through the 4-D maps), both storage orders of
+    the large operand (K-major slabs of any height, M-major slabs of 64 rows)."""
+    for types, (la, lb, lc) in [(1, (0, 1, 0)), (1, (0, 0, 0)), (2, (0, 1, 0)), (3, (1, 0, 0)), (0, (1, 1, 0))]:
+        if lb == 0 and N % 8:
+            continue
+        bf16 = types >= 2
+        A, B = seeded(M, N, K, la, lb, bf16)
+        ref = oracle.hgemm(types, A, B, M, N, K, lc, la, lb)
+        got = gpu_gemm(types, A, B, M, N, K, lc, la, lb)
+        check_parity(types, got, ref, K, SIGMA_UNIFORM, M, N, lc)
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 512, 4096), (768, 3072, 768), (1536, 1536, 512), (2048, 512, 2048), (384, 384, 384)])
+def test_sizes_without_a_table_entry(M, N, K):
+    """Sizes the tuned table does not hold: the borrowed entry is checked against the launch
+    path's cost model, which may pick another tile or partition K.  Whatever it picks must
+    give the reference's result."""
+    for types, (la, lb, lc) in [(3, (0, 1, 0)), (2, (0, 0, 0)), (1, (1, 1, 1)), (0, (1, 0, 0))]:
+        bf16 = types >= 2
+        A, B = seeded(M, N, K, la, lb, bf16)
+        ref = oracle.hgemm(types, A, B, M, N, K, lc, la, lb)
+        got = gpu_gemm(types, A, B, M, N, K, lc, la, lb)
+        check_parity(types, got, ref, K, SIGMA_UNIFORM, M, N, lc)
+
+
+def test_dependent_calls_back_to_back_and_in_a_graph():
+    """Every kernel is launched as a programmatic dependent of the kernel before it (its set-up
+    may overlap that kernel's tail).  A chain in which each GEMM reads what the previous one
+    wrote - plain, split-K and skinny calls mixed - must give bit-identical results whether the
+    calls are separated by synchronisation, issued back to back, or replayed from a CUDA graph."""
+    M = 1024
+    bf = torch.bfloat16
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    X0 = (torch.randn(M, M, device="cuda", generator=gen) * 0.05).to(bf)
+    W = [(torch.randn(M, M, device="cuda", generator=gen) * 0.05).to(bf) for _ in range(4)]
+    V = (torch.randn(16, M, device="cuda", generator=gen) * 0.05).to(bf)
+    l = loader()
+    split = g.GemmConfig(128, 128, 4, 1, 4, 0)
+
+    def chain(bufs, sync):
+        x = X0
+        for i, w in enumerate(W):
+            l.gemm(bufs[i], x, w, M, M, M, 0, 0, 1, types=2, config=split if i % 2 else None)
+            if sync:
+                torch.cuda.synchronize()
+            x = bufs[i]
+        l.gemm(bufs[4], V, x, 16, M, M, 0, 0, 1, types=2)  # skinny call reading the chain's end
+
+    def fresh():
+        return [torch.zeros(M, M, device="cuda", dtype=bf) for _ in range(4)] + [torch.zeros(16, M, device="cuda", dtype=bf)]
+
+    ref = fresh()
+    chain(ref, sync=True)
+    torch.cuda.synchronize()
+    b2b = fresh()
+    for _ in range(3):
+        chain(b2b, sync=False)
+    torch.cuda.synchronize()
+    for r, o in zip(ref, b2b):
+        assert torch.equal(r.view(torch.int16), o.view(torch.int16))
+    gb = fresh()
+    chain(gb, sync=False)  # warm the per-stream state before capture
+    torch.cuda.synchronize()
+    for t in gb:
+        t.zero_()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        chain(gb, sync=False)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert g.device_status() == 0
+    for r, o in zip(ref, gb):
+        assert torch.equal(r.view(torch.int16), o.view(torch.int16))
+    assert float(ref[4].float().abs().max()) > 0

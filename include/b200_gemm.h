@@ -123,6 +123,34 @@ int b200_gemm_ex(int types, void* C, const void* A, const void* B, size_t M, siz
 int b200_gemm_select_config(size_t M, size_t N, size_t K, int types, int layout_c, int layout_a,
                             int layout_b, b200_gemm_config* out);
 
+/* What a call with these arguments would launch (operands assumed 16-byte aligned): the
+ * kernel family, the tile it cuts the kernel view into, the K partitions, the ring geometry
+ * and the CTA count - after the table lookup, the check of a borrowed entry against the cost
+ * model, the narrow-tile and row-slab rules.  Pure host code: `sm_count` 0 means the current
+ * device's SM count, or 148 when the process has no usable device.  No reference counterpart
+ * (the reference's launch is fully described by its config entry,
+ * rocm_wmma_gemm/src/gemm.cpp:38-92). */
+enum b200_gemm_kernel_kind {
+    B200_GEMM_KERNEL_NONE       = 0, /* nothing to launch (empty C, or K == 0: C is zero-filled) */
+    B200_GEMM_KERNEL_GENERIC    = 1, /* CUDA-core kernel: a leading dimension TMA cannot address */
+    B200_GEMM_KERNEL_STAGED     = 2, /* tcgen05 kernel, TMA-store epilogue */
+    B200_GEMM_KERNEL_TRANSPOSED = 3  /* tcgen05 kernel on swapped operands, transposing epilogue (skinny problems) */
+};
+typedef struct b200_gemm_plan_info {
+    int       kernel;            /* b200_gemm_kernel_kind */
+    int       tile_m;            /* kernel-view rows per tile: 128 x cluster, or the slab height (8..128) */
+    int       tile_n;            /* kernel-view columns per tile */
+    int       cluster;           /* CTAs per tile (1 or 2) */
+    int       split_k;           /* K partitions (> 1: a reduction pass follows) */
+    int       slots;             /* ring depth */
+    int       k_blocks_per_slot; /* 64-deep k-blocks staged per ring slot (1, 2 or 4) */
+    int       raster;            /* tile-row band height (0: column sweep) */
+    int       ctas;              /* CTAs launched (persistent: at most one per SM) */
+    long long work_units;        /* tiles x K partitions x batch */
+} b200_gemm_plan_info;
+int b200_gemm_plan(int types, size_t M, size_t N, size_t K, size_t batch_count, int layout_c,
+                   int layout_a, int layout_b, int sm_count, b200_gemm_plan_info* out);
+
 /* Host-buffer call: A, B, C are HOST pointers (pageable or pinned).  Copies A and B to the
  * device, runs the GEMM, copies C back and synchronises; device buffers are cached per
  * device and grow on demand.  This is the path a caller without device memory of its own

@@ -5,7 +5,8 @@ Counterpart of the reference's benchmark binaries (benchmark/gemm/bench_{half_ha
 bf16_bf16,float_bf16}.cpp of adelj88/rocm_wmma_gemm): for every requested shape and each of the
 eight row/column-major combinations of A, B and C it times the GEMM with device events and
 reports TFLOP/s (2*M*N*K*batch / t, the reference's count), GB/s of algorithmic bytes, the
-fraction of the tensor and HBM rooflines, and the configuration the tuned table chose.
+fraction of the tensor and HBM rooflines, and the launch plan (`b200_gemm_plan`: kernel family,
+tile, K partitions, k-blocks per ring slot x slots, raster, CTAs).
 Benchmark names use the reference's format `{A:m_layout::row_major,B:...,C:...,m:..,n:..,k:..}`.
 
     python -m rocm_wmma_gemm_b200.bench_shapes --type f16_f16 --shapes 1024,1024,1024 8192,8192,8192
@@ -143,7 +144,7 @@ def main(argv=None):
     out = open(a.json, "a") if a.json else None
     print(f"# {torch.cuda.get_device_name(0)}  type={spec['type']} fill={spec['fill']} batch={a.batch_count} "
           f"(peaks: {peaks.get('bf16_tflops')} TFLOP/s burst, {peaks.get('hbm_gbs')} GB/s measured; nominal 2250 / 8000)")
-    print(f"{'benchmark':86s} {'min ms':>9s} {'med ms':>9s} {'TFLOP/s':>8s} {'sustained':>9s} {'graph':>8s} {'GB/s':>7s} {'%tensor':>7s} {'%hbm':>6s}  config")
+    print(f"{'benchmark':86s} {'min ms':>9s} {'med ms':>9s} {'TFLOP/s':>8s} {'sustained':>9s} {'graph':>8s} {'GB/s':>7s} {'%tensor':>7s} {'%hbm':>6s}  launch plan")
     print("# TFLOP/s: median of individually timed calls (host launch cost included, as the reference times them); sustained: "
           "back-to-back calls; graph: the same launches replayed from a CUDA graph (device time only)")
     for (M, N, K) in spec["shapes"]:
@@ -153,6 +154,7 @@ def main(argv=None):
             nbytes = (in_sz * (M * K + K * N) + out_sz * M * N) * a.batch_count
             med = statistics.median(ms)
             cfg, idx = g.get_gemm_params(M, N, K, lc, la, lb, 1 if types in (1, 3) else 0)
+            plan = g.plan(M, N, K, lc, la, lb, types=types, batch_count=a.batch_count)  # what actually launches
             name = f"{{A:{LAYOUT[la]},B:{LAYOUT[lb]},C:{LAYOUT[lc]},m:{M},n:{N},k:{K}}}"
             rec = {"name": name, "type": spec["type"], "fill": spec["fill"], "batch": a.batch_count, "M": M, "N": N, "K": K,
                    "layout": {"A": la, "B": lb, "C": lc}, "min_time_ms": ms[0], "median_time_ms": med, "max_time_ms": ms[-1],
@@ -165,10 +167,10 @@ def main(argv=None):
                    "pct_of_measured_tensor": 100 * flops / (med * 1e-3) / 1e12 / peaks["bf16_tflops"],
                    "pct_of_nominal_hbm": 100 * nbytes / (med * 1e-3) / 1e9 / NOMINAL_GBS,
                    "pct_of_measured_hbm": 100 * nbytes / (med * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                   "config": cfg.as_dict(), "config_index": idx}
+                   "config": cfg.as_dict(), "config_index": idx, "plan": plan.as_dict()}
             print(f"{name:86s} {ms[0]:9.4f} {med:9.4f} {rec['tflops_median']:8.1f} {rec['tflops_sustained']:9.1f} "
                   f"{(rec['tflops_graph'] or 0):8.1f} {rec['gbs_median']:7.0f} {rec['pct_of_nominal_tensor']:7.1f} {rec['pct_of_nominal_hbm']:6.1f}  "
-                  f"{cfg.tile_m}x{cfg.tile_n} s{cfg.stages} k{cfg.split_k} r{cfg.raster}", flush=True)
+                  f"{plan.short()}", flush=True)
             if out:
                 out.write(json.dumps(rec) + "\n")
                 out.flush()

@@ -672,28 +672,28 @@ static cudaError_t launch_reduce(int out, unsigned blocks, cudaStream_t s, const
     }
 }
 
-static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_config* user_cfg)
+// Everything the launch path decides before it touches the GPU.
+struct LaunchPlan {
+    bool             generic    = false; // TMA cannot address the problem: CUDA-core kernel
+    bool             transposed = false; // operands swapped once more, transposing epilogue
+    bool             narrow     = false; // kernel view of at most 64 columns (or transposed)
+    bool             slot       = false; // one-CTA kernel with kc k-blocks per ring slot
+    bool             k4d        = false; // K-major operands through the 4-D (chunked K) maps
+    View             v{};
+    b200_gemm_config cfg{};
+    uint32_t         bm = BLOCK_M, kc = 1, kb_per_split = 0;
+};
+
+static int make_plan(const Problem& p, const b200_gemm_config* user_cfg, int sm_count, LaunchPlan* out)
 {
-    int st = validate(p);
-    if (st != B200_GEMM_OK) return st;
-    if (p.M == 0 || p.N == 0) return B200_GEMM_OK;
-
-    DeviceCtx* ctx = nullptr;
-    st             = get_ctx(&ctx);
-    if (st != B200_GEMM_OK) return st;
-
-    const size_t out_sz = out_is_f32(p.types) ? 4 : 2;
-    if (p.K == 0) { // empty sum: C = 0
-        CUDA_TRY(cudaMemsetAsync(p.C, 0, p.M * p.N * p.batch * out_sz, stream));
-        return B200_GEMM_OK;
-    }
-
-    View v = make_view(p);
+    LaunchPlan pl;
+    View&      v = pl.v;
+    v            = make_view(p);
     // Skinny problems: the MMA's M extent is fixed at 128 rows but its N extent goes down to 16,
     // so when the kernel view has few rows and many columns the operands swap roles once more
     // (the kernel computes D^T) and the epilogue writes D^T transposed, i.e. D.  No 128-row
     // tile of mostly zero-filled A' is staged and the ring holds twice as many slots.
-    bool transposed = false;
+    bool& transposed = pl.transposed;
     if (v.M <= 64 && v.N >= 128 && operands_tma_ok(p, v) && reinterpret_cast<uintptr_t>(v.d) % 16 == 0 &&
         ((size_t)v.M * v.N) % 4 == 0) {
         std::swap(v.a, v.b);
@@ -702,26 +702,22 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
         transposed = true;
     }
     if (!transposed && !tma_ok(p, v)) {
-        cudaError_t e;
-        switch (p.types) {
-            case B200_GEMM_F16_F16: e = launch_generic<__half, __half>(p, stream); break;
-            case B200_GEMM_F32_F16: e = launch_generic<__half, float>(p, stream); break;
-            case B200_GEMM_BF16_BF16: e = launch_generic<__nv_bfloat16, __nv_bfloat16>(p, stream); break;
-            default: e = launch_generic<__nv_bfloat16, float>(p, stream); break;
-        }
-        if (e != cudaSuccess) return fail(B200_GEMM_ERR_CUDA, "generic kernel launch failed: %s", cudaGetErrorString(e));
+        pl.generic = true;
+        *out       = pl;
         return B200_GEMM_OK;
     }
 
-    bool             tuned = true;
-    b200_gemm_config cfg   = resolve_config(p, user_cfg, nullptr, &tuned);
-    st                     = check_config(cfg);
+    bool              tuned = true;
+    b200_gemm_config& cfg   = pl.cfg;
+    cfg                     = resolve_config(p, user_cfg, nullptr, &tuned);
+    int st                  = check_config(cfg);
     if (st != B200_GEMM_OK) return st;
-    if (!tuned) adapt_config(cfg, v, p.batch, ctx->sm_count);
+    if (!tuned) adapt_config(cfg, v, p.batch, sm_count);
     // Narrow kernel views (at most 64 columns) run on the narrow one-CTA variants whatever
     // tile the table names: tile_n is the smallest compiled width that covers N (an MN-major
     // B' is loaded in 64-row boxes, so it needs 64) and the ring is as deep as fits.
     const bool narrow = v.N <= 64 || transposed;
+    pl.narrow         = narrow;
     if (narrow) {
         cfg.tile_m  = BLOCK_M;
         cfg.cluster = 1;
@@ -733,9 +729,9 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     // streams the same number of bytes, no K partition and no reduction pass is needed.  (The
     // MMA still spans 128 rows; the rows past the slab are never stored.)  An M-major A' is
     // loaded in 64-row boxes, so its slabs are 64 or 128 rows.
-    uint32_t bm = BLOCK_M;
+    uint32_t& bm = pl.bm;
     if (transposed && !user_cfg) {
-        const uint32_t sms       = (uint32_t)ctx->sm_count;
+        const uint32_t sms       = (uint32_t)sm_count;
         const uint32_t step      = v.a_mn ? 64u : 8u;
         uint64_t       best_cost = ~0ull;
         uint32_t       best_bm = 0, best_tiles = 0;
@@ -754,7 +750,7 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
             cfg.split_k = 1;
         }
     }
-    uint32_t kb_per_split = 0;
+    uint32_t& kb_per_split = pl.kb_per_split;
     legalize(cfg, v, &kb_per_split);
     if (!user_cfg && cfg.split_k > 1 && !transposed && v.N % 4) { // the table's nearest entry may not fit
         cfg.split_k = 1;
@@ -766,9 +762,10 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     // slot; at least three slots must fit.  K-major operands fetch a slot with one 4-D box over
     // a [chunk][row][64] view of the matrix, which needs K to be a multiple of 64.
     const bool slot = cfg.cluster == 1 && cfg.tile_n <= 256;
-    uint32_t   kc   = 1;
-    const bool k4d  = slot && v.K % BLOCK_K == 0;
-    if (slot && (k4d || (v.a_mn && v.b_mn))) {
+    pl.slot         = slot;
+    uint32_t& kc    = pl.kc;
+    pl.k4d          = slot && v.K % BLOCK_K == 0;
+    if (slot && (pl.k4d || (v.a_mn && v.b_mn))) {
         kc = cfg.tile_n >= 256 ? 1u : (cfg.tile_n >= 128 ? 2u : 4u);
         auto slots_fit = [&](uint32_t c) {
             return transposed ? slab_max_stages((int)bm, cfg.tile_n, (int)c) : slot_max_stages(cfg.tile_n, (int)c);
@@ -782,6 +779,49 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     }
     if (transposed) cfg.stages = slab_max_stages((int)bm, cfg.tile_n, (int)kc);
     else if (slot && (narrow || kc > 1)) cfg.stages = slot_max_stages(cfg.tile_n, (int)kc);
+    *out = pl;
+    return B200_GEMM_OK;
+}
+
+static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_config* user_cfg)
+{
+    int st = validate(p);
+    if (st != B200_GEMM_OK) return st;
+    if (p.M == 0 || p.N == 0) return B200_GEMM_OK;
+
+    DeviceCtx* ctx = nullptr;
+    st             = get_ctx(&ctx);
+    if (st != B200_GEMM_OK) return st;
+
+    const size_t out_sz = out_is_f32(p.types) ? 4 : 2;
+    if (p.K == 0) { // empty sum: C = 0
+        CUDA_TRY(cudaMemsetAsync(p.C, 0, p.M * p.N * p.batch * out_sz, stream));
+        return B200_GEMM_OK;
+    }
+
+    LaunchPlan pl;
+    st = make_plan(p, user_cfg, ctx->sm_count, &pl);
+    if (st != B200_GEMM_OK) return st;
+    if (pl.generic) {
+        cudaError_t e;
+        switch (p.types) {
+            case B200_GEMM_F16_F16: e = launch_generic<__half, __half>(p, stream); break;
+            case B200_GEMM_F32_F16: e = launch_generic<__half, float>(p, stream); break;
+            case B200_GEMM_BF16_BF16: e = launch_generic<__nv_bfloat16, __nv_bfloat16>(p, stream); break;
+            default: e = launch_generic<__nv_bfloat16, float>(p, stream); break;
+        }
+        if (e != cudaSuccess) return fail(B200_GEMM_ERR_CUDA, "generic kernel launch failed: %s", cudaGetErrorString(e));
+        return B200_GEMM_OK;
+    }
+    const View&             v            = pl.v;
+    const b200_gemm_config& cfg          = pl.cfg;
+    const bool              transposed   = pl.transposed;
+    const bool              narrow       = pl.narrow;
+    const bool              slot         = pl.slot;
+    const bool              k4d          = pl.k4d;
+    const uint32_t          bm           = pl.bm;
+    const uint32_t          kc           = pl.kc;
+    const uint32_t          kb_per_split = pl.kb_per_split;
 
     const int      bn   = cfg.tile_n;
     const int      out  = out_kind(p.types);
@@ -1157,17 +1197,72 @@ extern "C" int b200_gemm_select_config(size_t M, size_t N, size_t K, int types, 
     return i;
 }
 
+// SM count the planning functions assume: the current device's, or a B200's 148 when the
+// process has no usable device (the functions are pure host code).
+static int planning_sm_count(int requested)
+{
+    if (requested > 0) return requested;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0)
+        return sms;
+    (void)cudaGetLastError();
+    return 148;
+}
+
+// A problem with stand-in, 256-byte aligned operand addresses (planning never dereferences them).
+static Problem planning_problem(int types, size_t M, size_t N, size_t K, size_t batch, int lc, int la, int lb)
+{
+    return Problem{types, reinterpret_cast<void*>(uintptr_t(0x1000)), reinterpret_cast<const void*>(uintptr_t(0x2000)),
+                   reinterpret_cast<const void*>(uintptr_t(0x3000)), M, N, K, batch, lc, la, lb};
+}
+
 extern "C" size_t b200_gemm_workspace_bytes(int types, size_t M, size_t N, size_t K, size_t batch_count,
                                             int layout_c, int layout_a, int layout_b,
                                             const b200_gemm_config* user)
 {
-    const Problem p{types, nullptr, nullptr, nullptr, M, N, K, batch_count, layout_c, layout_a, layout_b};
-    if (types < 0 || types > 3 || ((layout_c | layout_a | layout_b) & ~1) || M == 0 || N == 0 || K == 0) return 0;
-    b200_gemm_config cfg = resolve_config(p, user, nullptr);
-    const View       v   = make_view(p);
-    uint32_t         per = 0;
-    legalize(cfg, v, &per);
-    return cfg.split_k > 1 ? batch_count * cfg.split_k * M * N * sizeof(float) : 0;
+    if (types < 0 || types > 3 || ((layout_c | layout_a | layout_b) & ~1) || M == 0 || N == 0 || K == 0 || batch_count == 0)
+        return 0;
+    const Problem p = planning_problem(types, M, N, K, batch_count, layout_c, layout_a, layout_b);
+    LaunchPlan    pl;
+    if (make_plan(p, user, planning_sm_count(0), &pl) != B200_GEMM_OK || pl.generic) return 0;
+    return pl.cfg.split_k > 1 ? batch_count * (size_t)pl.cfg.split_k * M * N * sizeof(float) : 0;
+}
+
+extern "C" int b200_gemm_plan(int types, size_t M, size_t N, size_t K, size_t batch_count, int layout_c,
+                              int layout_a, int layout_b, int sm_count, b200_gemm_plan_info* out)
+{
+    t_last_status = B200_GEMM_OK;
+    if (!out) return fail(B200_GEMM_ERR_NULL_POINTER, "out is NULL");
+    const Problem p  = planning_problem(types, M, N, K, batch_count, layout_c, layout_a, layout_b);
+    int           st = validate(p);
+    if (st != B200_GEMM_OK) return st;
+    *out = b200_gemm_plan_info{};
+    if (M == 0 || N == 0 || K == 0) return B200_GEMM_OK; // nothing is launched (K == 0: a memset)
+    const int  sms = planning_sm_count(sm_count);
+    LaunchPlan pl;
+    st = make_plan(p, nullptr, sms, &pl);
+    if (st != B200_GEMM_OK) return st;
+    if (pl.generic) {
+        out->kernel = B200_GEMM_KERNEL_GENERIC;
+        return B200_GEMM_OK;
+    }
+    const uint32_t cl      = (uint32_t)pl.cfg.cluster;
+    const uint32_t tile_m  = pl.transposed ? pl.bm : (uint32_t)BLOCK_M * cl;
+    const uint64_t m_tiles = (pl.v.M + tile_m - 1) / tile_m;
+    const uint64_t n_tiles = (pl.v.N + pl.cfg.tile_n - 1) / pl.cfg.tile_n;
+    const uint64_t work    = m_tiles * n_tiles * batch_count * (uint64_t)pl.cfg.split_k;
+    out->kernel            = pl.transposed ? B200_GEMM_KERNEL_TRANSPOSED : B200_GEMM_KERNEL_STAGED;
+    out->tile_m            = (int)tile_m;
+    out->tile_n            = pl.cfg.tile_n;
+    out->cluster           = pl.cfg.cluster;
+    out->split_k           = pl.cfg.split_k;
+    out->slots             = pl.cfg.stages;
+    out->k_blocks_per_slot = (int)pl.kc;
+    out->raster            = pl.cfg.raster;
+    out->ctas              = (int)(cl * std::min<uint64_t>(work, (uint64_t)sms / cl));
+    out->work_units        = (long long)work;
+    return B200_GEMM_OK;
 }
 
 extern "C" int b200_gemm_slab(size_t N, int world, int rank, size_t align, size_t* n_begin, size_t* n_count)

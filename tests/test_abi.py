@@ -121,3 +121,39 @@ def test_explicit_config_is_validated(gemm_lib):
 def test_version_and_counters(gemm_lib):
     assert b"sm_100a" in gemm_lib.lib().b200_gemm_version()
     assert gemm_lib.launch_count() >= 0
+
+
+def test_launch_plan_rules():
+    """b200_gemm_plan is host code: the launch rules can be checked without a GPU (148 SMs given)."""
+    import rocm_wmma_gemm_b200 as g
+    # skinny, large operand K-major: operands swapped, 147 slabs of 56 rows, K not partitioned,
+    # four k-blocks per ring slot
+    p = g.plan(16, 8192, 8192, 0, 0, 1, types=1, sm_count=148)
+    assert (p.kernel, p.tile_m, p.tile_n, p.split_k, p.k_blocks_per_slot, p.ctas) == (3, 56, 16, 1, 4, 147)
+    assert p.slots >= 3
+    # two waves of 104-row slabs
+    p = g.plan(16, 28672, 8192, 0, 0, 1, types=1, sm_count=148)
+    assert (p.kernel, p.tile_m, p.split_k, p.work_units, p.ctas) == (3, 104, 1, 276, 148)
+    # large operand M-major (B row-major): slabs are whole 64-row boxes
+    p = g.plan(16, 8192, 8192, 0, 0, 0, types=1, sm_count=148)
+    assert p.kernel == 3 and p.tile_m in (64, 128)
+    # K not a multiple of 64: one k-block per slot (plain 3-D maps)
+    assert g.plan(16, 8192, 8200, 0, 0, 1, types=1, sm_count=148).k_blocks_per_slot == 1
+    # column-major C of a skinny problem: the narrow staged-epilogue variant, no operand swap
+    p = g.plan(16, 8192, 8192, 1, 0, 1, types=1, sm_count=148)
+    assert (p.kernel, p.tile_m, p.tile_n, p.cluster) == (2, 128, 16, 1)
+    # the headline size runs on CTA pairs, one k-block per slot, every SM busy
+    p = g.plan(8192, 8192, 8192, 0, 0, 1, types=3, sm_count=148)
+    assert (p.kernel, p.cluster, p.tile_m, p.k_blocks_per_slot, p.ctas) == (2, 2, 256, 1, 148) and p.tile_n in (256, 512)
+    # a size without a table entry that the nearest entry would under-fill: smaller tile and/or K partitions
+    p = g.plan(512, 512, 4096, 0, 0, 1, types=2, sm_count=148)
+    assert p.kernel == 2 and p.ctas >= 74
+    # leading dimensions TMA cannot address -> the CUDA-core kernel; empty problems launch nothing
+    assert g.plan(100, 100, 100, sm_count=148).kernel == 1
+    assert g.plan(0, 100, 100, sm_count=148).kernel == 0
+    # the workspace query agrees with the plan
+    lib = g.lib()
+    for (m, n, k, t) in [(16, 8192, 8192, 1), (128, 8192, 8192, 1), (512, 512, 4096, 2), (8192, 8192, 8192, 3)]:
+        p = g.plan(m, n, k, 0, 0, 1, types=t)
+        want = p.split_k * m * n * 4 if p.split_k > 1 else 0
+        assert lib.b200_gemm_workspace_bytes(t, m, n, k, 1, 0, 0, 1, None) == want

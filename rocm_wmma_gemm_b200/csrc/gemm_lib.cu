@@ -166,7 +166,7 @@ struct DeviceCtx {
     std::vector<Workspace> workspaces;
     // host-buffer path: compute stream, copy-in / copy-out streams and the events chaining them
     cudaStream_t h_in = nullptr, h_out = nullptr;
-    cudaEvent_t  h_ev_in[16] = {}, h_ev_done[16] = {}, h_ev_b = nullptr;
+    cudaEvent_t  h_ev_a[16] = {}, h_ev_b[16] = {}, h_ev_done[256] = {};
     cudaStream_t h_stream = nullptr;
     void*        h_buf[3] = {nullptr, nullptr, nullptr};
     size_t       h_cap[3] = {0, 0, 0};
@@ -1307,67 +1307,93 @@ extern "C" int b200_gemm_host(int types, void* C, const void* A, const void* B, 
     }
     cudaStream_t s = ctx->h_stream;
 
-    // Large single problems are pipelined: the operand that is not chunked goes up first, then
-    // chunks of the other operand (rows of A, or columns of B) are copied in, multiplied and
-    // their slice of C copied out on three streams, so the upload, the GEMMs and the download
-    // overlap (PCIe is full duplex).  Every chunk is stored densely on the device, so each
-    // chunk is an ordinary dense GEMM whatever the layouts.
-    const bool   by_rows  = M >= N;
-    const size_t dim      = by_rows ? M : N;
-    size_t       nchunks  = std::min<size_t>(8, dim / 512);
-    if (batch_count == 1 && nchunks >= 2 && bytes[0] + bytes[1] + bytes[2] >= (32u << 20) && K > 0) {
+    // Large single problems are pipelined in two dimensions: A goes up in chunks of rows, B in
+    // chunks of columns, alternately; a tile of C is computed as soon as its row chunk and its
+    // column chunk are on the device and goes down while later chunks still come up (PCIe is
+    // full duplex).  The first tile starts after 1/8 of A and 1/8 of B.  (Cutting the last
+    // chunks finer, so that fewer tiles are left once the uploads end, was measured slower.)
+    // Chunks and tiles are stored densely on the device, so every tile is an ordinary dense
+    // GEMM whatever the layouts; strided sides are host-side 2-D copies.
+    auto chunk_starts = [](size_t dim) { // chunk boundaries, multiples of 256 (last one = dim)
+        std::vector<size_t> b{0};
+        if (dim < 2048) {
+            b.push_back(dim);
+            return b;
+        }
+        const size_t step = ((dim + 7) / 8 + 255) / 256 * 256;
+        size_t       at   = 0;
+        while (dim - at > step) b.push_back(at += step);
+        b.push_back(dim);
+        return b;
+    };
+    const std::vector<size_t> rb = chunk_starts(M), cb = chunk_starts(N);
+    const size_t              nra = rb.size() - 1, ncb = cb.size() - 1;
+    if (batch_count == 1 && nra * ncb >= 2 && bytes[0] + bytes[1] + bytes[2] >= (32u << 20) && K > 0) {
         {
             std::lock_guard<std::mutex> lock(g_mutex);
             if (!ctx->h_in) {
                 CUDA_TRY(cudaStreamCreateWithFlags(&ctx->h_in, cudaStreamNonBlocking));
                 CUDA_TRY(cudaStreamCreateWithFlags(&ctx->h_out, cudaStreamNonBlocking));
-                CUDA_TRY(cudaEventCreateWithFlags(&ctx->h_ev_b, cudaEventDisableTiming));
                 for (int i = 0; i < 16; ++i) {
-                    CUDA_TRY(cudaEventCreateWithFlags(&ctx->h_ev_in[i], cudaEventDisableTiming));
-                    CUDA_TRY(cudaEventCreateWithFlags(&ctx->h_ev_done[i], cudaEventDisableTiming));
+                    CUDA_TRY(cudaEventCreateWithFlags(&ctx->h_ev_a[i], cudaEventDisableTiming));
+                    CUDA_TRY(cudaEventCreateWithFlags(&ctx->h_ev_b[i], cudaEventDisableTiming));
                 }
+                for (int i = 0; i < 256; ++i) CUDA_TRY(cudaEventCreateWithFlags(&ctx->h_ev_done[i], cudaEventDisableTiming));
             }
         }
-        const size_t step = ((dim + nchunks - 1) / nchunks + 255) / 256 * 256;
-        char*        dA   = static_cast<char*>(ctx->h_buf[0]);
-        char*        dB   = static_cast<char*>(ctx->h_buf[1]);
-        char*        dC   = static_cast<char*>(ctx->h_buf[2]);
-        const char*  hA   = static_cast<const char*>(A);
-        const char*  hB   = static_cast<const char*>(B);
-        char*        hC   = static_cast<char*>(C);
-        // the whole of the operand that is not chunked
-        if (by_rows) CUDA_TRY(cudaMemcpyAsync(dB, hB, bytes[1], cudaMemcpyHostToDevice, ctx->h_in));
-        else CUDA_TRY(cudaMemcpyAsync(dA, hA, bytes[0], cudaMemcpyHostToDevice, ctx->h_in));
-        size_t ci = 0;
-        for (size_t c0 = 0; c0 < dim; c0 += step, ++ci) {
-            const size_t cn = std::min(step, dim - c0);
-            if (by_rows) { // rows [c0, c0 + cn) of A and C
-                char* dAc = dA + c0 * K * 2;
-                if (layout_a == 0) CUDA_TRY(cudaMemcpyAsync(dAc, hA + c0 * K * 2, cn * K * 2, cudaMemcpyHostToDevice, ctx->h_in));
-                else CUDA_TRY(cudaMemcpy2DAsync(dAc, cn * 2, hA + c0 * 2, M * 2, cn * 2, K, cudaMemcpyHostToDevice, ctx->h_in));
-            } else { // columns [c0, c0 + cn) of B and C
-                char* dBc = dB + c0 * K * 2;
-                if (layout_b == 1) CUDA_TRY(cudaMemcpyAsync(dBc, hB + c0 * K * 2, cn * K * 2, cudaMemcpyHostToDevice, ctx->h_in));
-                else CUDA_TRY(cudaMemcpy2DAsync(dBc, cn * 2, hB + c0 * 2, N * 2, cn * 2, K, cudaMemcpyHostToDevice, ctx->h_in));
+        char*        dA    = static_cast<char*>(ctx->h_buf[0]);
+        char*        dB    = static_cast<char*>(ctx->h_buf[1]);
+        char*        dC    = static_cast<char*>(ctx->h_buf[2]);
+        const char*  hA    = static_cast<const char*>(A);
+        const char*  hB    = static_cast<const char*>(B);
+        char*        hC    = static_cast<char*>(C);
+        size_t       ntile = 0;
+        auto tile = [&](size_t i, size_t j) -> int {
+            const size_t r0 = rb[i], rn = rb[i + 1] - r0;
+            const size_t c0 = cb[j], cn = cb[j + 1] - c0;
+            CUDA_TRY(cudaStreamWaitEvent(s, ctx->h_ev_a[i], 0));
+            CUDA_TRY(cudaStreamWaitEvent(s, ctx->h_ev_b[j], 0));
+            // tiles of row chunk i are packed one after the other behind the chunks before it
+            char*         dT = dC + (r0 * N + rn * c0) * out_sz;
+            const Problem tp{types, dT, dA + r0 * K * 2, dB + c0 * K * 2, rn, cn, K, 1, layout_c, layout_a, layout_b};
+            const int     ts = run_gemm(tp, s, nullptr);
+            if (ts != B200_GEMM_OK) return ts;
+            cudaEvent_t done = ctx->h_ev_done[ntile++];
+            CUDA_TRY(cudaEventRecord(done, s));
+            CUDA_TRY(cudaStreamWaitEvent(ctx->h_out, done, 0));
+            if (layout_c == 0)
+                CUDA_TRY(cudaMemcpy2DAsync(hC + (r0 * N + c0) * out_sz, N * out_sz, dT, cn * out_sz, cn * out_sz, rn,
+                                           cudaMemcpyDeviceToHost, ctx->h_out));
+            else
+                CUDA_TRY(cudaMemcpy2DAsync(hC + (c0 * M + r0) * out_sz, M * out_sz, dT, rn * out_sz, rn * out_sz, cn,
+                                           cudaMemcpyDeviceToHost, ctx->h_out));
+            return B200_GEMM_OK;
+        };
+        for (size_t t = 0; t < std::max(nra, ncb); ++t) {
+            if (t < nra) { // rows [r0, r0 + rn) of A
+                const size_t r0 = rb[t], rn = rb[t + 1] - r0;
+                char*        d  = dA + r0 * K * 2;
+                if (layout_a == 0) CUDA_TRY(cudaMemcpyAsync(d, hA + r0 * K * 2, rn * K * 2, cudaMemcpyHostToDevice, ctx->h_in));
+                else CUDA_TRY(cudaMemcpy2DAsync(d, rn * 2, hA + r0 * 2, M * 2, rn * 2, K, cudaMemcpyHostToDevice, ctx->h_in));
+                CUDA_TRY(cudaEventRecord(ctx->h_ev_a[t], ctx->h_in));
             }
-            CUDA_TRY(cudaEventRecord(ctx->h_ev_in[ci], ctx->h_in));
-            CUDA_TRY(cudaStreamWaitEvent(s, ctx->h_ev_in[ci], 0));
-            char* dCc = dC + (by_rows ? c0 * N : c0 * M) * out_sz;
-            const Problem cp = by_rows ? Problem{types, dCc, dA + c0 * K * 2, dB, cn, N, K, 1, layout_c, layout_a, layout_b}
-                                       : Problem{types, dCc, dA, dB + c0 * K * 2, M, cn, K, 1, layout_c, layout_a, layout_b};
-            st = run_gemm(cp, s, nullptr);
+            if (t < ncb) { // columns [c0, c0 + cn) of B
+                const size_t c0 = cb[t], cn = cb[t + 1] - c0;
+                char*        d  = dB + c0 * K * 2;
+                if (layout_b == 1) CUDA_TRY(cudaMemcpyAsync(d, hB + c0 * K * 2, cn * K * 2, cudaMemcpyHostToDevice, ctx->h_in));
+                else CUDA_TRY(cudaMemcpy2DAsync(d, cn * 2, hB + c0 * 2, N * 2, cn * 2, K, cudaMemcpyHostToDevice, ctx->h_in));
+                CUDA_TRY(cudaEventRecord(ctx->h_ev_b[t], ctx->h_in));
+            }
+            // the tiles the two new chunks complete: row chunk t x columns 0..t, rows 0..t-1 x column chunk t
+            if (t < nra)
+                for (size_t j = 0; j <= std::min(t, ncb - 1); ++j)
+                    if ((st = tile(t, j)) != B200_GEMM_OK) break;
+            if (st == B200_GEMM_OK && t < ncb)
+                for (size_t i = 0; i < std::min(t, nra); ++i)
+                    if ((st = tile(i, t)) != B200_GEMM_OK) break;
             if (st != B200_GEMM_OK) {
                 cudaDeviceSynchronize();
                 return st;
-            }
-            CUDA_TRY(cudaEventRecord(ctx->h_ev_done[ci], s));
-            CUDA_TRY(cudaStreamWaitEvent(ctx->h_out, ctx->h_ev_done[ci], 0));
-            if (by_rows) {
-                if (layout_c == 0) CUDA_TRY(cudaMemcpyAsync(hC + c0 * N * out_sz, dCc, cn * N * out_sz, cudaMemcpyDeviceToHost, ctx->h_out));
-                else CUDA_TRY(cudaMemcpy2DAsync(hC + c0 * out_sz, M * out_sz, dCc, cn * out_sz, cn * out_sz, N, cudaMemcpyDeviceToHost, ctx->h_out));
-            } else {
-                if (layout_c == 1) CUDA_TRY(cudaMemcpyAsync(hC + c0 * M * out_sz, dCc, M * cn * out_sz, cudaMemcpyDeviceToHost, ctx->h_out));
-                else CUDA_TRY(cudaMemcpy2DAsync(hC + c0 * out_sz, N * out_sz, dCc, cn * out_sz, cn * out_sz, M, cudaMemcpyDeviceToHost, ctx->h_out));
             }
         }
         CUDA_TRY(cudaStreamSynchronize(ctx->h_out));

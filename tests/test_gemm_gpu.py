@@ -356,13 +356,15 @@ def test_concurrent_streams_and_threads():
             check_parity(3, out, ref, K, SIGMA_UNIFORM, M, N, 0)
 
 
-SLAB_EDGES = [(16, 8200, 576), (33, 9000, 264), (64, 8192 + 56, 320), (8, 20000, 192), (16, 8192, 4096 + 64)]
+SLAB_EDGES = [(16, 8200, 576), (33, 9000, 264), (64, 8192 + 56, 320), (8, 20000, 192), (16, 8192, 4096 + 64),
+              # 65..128 rows: too tall for the operand swap, the staged-epilogue kernels with K partitions
+              (128, 8192, 576), (96, 9000, 264), (128, 2048, 4096 + 64), (100, 4096, 1024), (72, 1024, 128), (128, 16384 + 8, 64)]
 
 
 @pytest.mark.parametrize("M,N,K", SLAB_EDGES)
 def test_row_slab_edges(M, N, K):
     """Skinny problems wide enough for the row-slab partition (147+ slabs of 8..128 rows of the
-    large operand): ragged last slab, K not a multiple of 64 (one k-block per ring slot, plain
+    large operand), and their neighbours just above the 64-row limit of the operand swap: ragged last slab, K not a multiple of 64 (one k-block per ring slot, plain
     3-D maps) and long K (four k-blocks per slot through the 4-D maps), both storage orders of
     the large operand (K-major slabs of any height, M-major slabs of 64 rows)."""
     for types, (la, lb, lc) in [(1, (0, 1, 0)), (1, (0, 0, 0)), (2, (0, 1, 0)), (3, (1, 0, 0)), (0, (1, 1, 0))]:

@@ -682,7 +682,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             if (!ok) break;
             ptx::tc_fence_after();
             const uint32_t row0     = c.m0 + rank * BLOCK_M + q * 32u;
-            const bool     row_live = row0 < p.M;
+            // 32-row groups at and beyond the slab height belong to the next tile (narrow staged
+            // tiles may use slabs of 32, 64 or 96 rows; p.bm is 128 everywhere else).
+            const bool     row_live = row0 < p.M && q * 32u < p.bm;
             const uint32_t tacc = tmem_base + ((q * 32u) << 16) + buf * ACC_COLS + colh;
             if constexpr (TR) {
                 // Transposed epilogue: D(i, j) goes to out[j * M + i].  Each lane owns row i, so

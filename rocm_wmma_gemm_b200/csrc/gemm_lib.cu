@@ -729,10 +729,13 @@ static int make_plan(const Problem& p, const b200_gemm_config* user_cfg, int sm_
     // streams the same number of bytes, no K partition and no reduction pass is needed.  (The
     // MMA still spans 128 rows; the rows past the slab are never stored.)  An M-major A' is
     // loaded in 64-row boxes, so its slabs are 64 or 128 rows.
+    // The narrow staged-epilogue tiles (a skinny problem with a column-major C) stream the large
+    // operand the same way; their epilogue stores whole 32-row groups, so their slabs are
+    // multiples of 32 rows.
     uint32_t& bm = pl.bm;
-    if (transposed && !user_cfg) {
+    if (narrow && !user_cfg && (transposed || !v.a_mn)) { // (staged tiles on an M-major operand: measured slower)
         const uint32_t sms       = (uint32_t)sm_count;
-        const uint32_t step      = v.a_mn ? 64u : 8u;
+        const uint32_t step      = v.a_mn ? 64u : (transposed ? 8u : 32u);
         uint64_t       best_cost = ~0ull;
         uint32_t       best_bm = 0, best_tiles = 0;
         for (uint32_t cand = step; cand <= (uint32_t)BLOCK_M; cand += step) {
@@ -837,7 +840,7 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     gp.bm           = bm;
     gp.kc           = kc;
     gp.k4d          = k4d ? 1u : 0u;
-    gp.m_tiles      = transposed ? (v.M + bm - 1) / bm : (v.M + BLOCK_M * cl - 1) / (BLOCK_M * cl);
+    gp.m_tiles      = slot ? (v.M + bm - 1) / bm : (v.M + BLOCK_M * cl - 1) / (BLOCK_M * cl);
     gp.n_tiles      = (v.N + bn - 1) / bn;
     gp.k_blocks     = (v.K + BLOCK_K - 1) / BLOCK_K;
     gp.split_k      = split;
@@ -1248,7 +1251,7 @@ extern "C" int b200_gemm_plan(int types, size_t M, size_t N, size_t K, size_t ba
         return B200_GEMM_OK;
     }
     const uint32_t cl      = (uint32_t)pl.cfg.cluster;
-    const uint32_t tile_m  = pl.transposed ? pl.bm : (uint32_t)BLOCK_M * cl;
+    const uint32_t tile_m  = pl.slot ? pl.bm : (uint32_t)BLOCK_M * cl;
     const uint64_t m_tiles = (pl.v.M + tile_m - 1) / tile_m;
     const uint64_t n_tiles = (pl.v.N + pl.cfg.tile_n - 1) / pl.cfg.tile_n;
     const uint64_t work    = m_tiles * n_tiles * batch_count * (uint64_t)pl.cfg.split_k;

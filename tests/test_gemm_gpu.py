@@ -367,7 +367,9 @@ def test_row_slab_edges(M, N, K):
     large operand), and their neighbours just above the 64-row limit of the operand swap: ragged last slab, K not a multiple of 64 (one k-block per ring slot, plain
     3-D maps) and long K (four k-blocks per slot through the 4-D maps), both storage orders of
     the large operand (K-major slabs of any height, M-major slabs of 64 rows)."""
-    for types, (la, lb, lc) in [(1, (0, 1, 0)), (1, (0, 0, 0)), (2, (0, 1, 0)), (3, (1, 0, 0)), (0, (1, 1, 0))]:
+    for types, (la, lb, lc) in [(1, (0, 1, 0)), (1, (0, 0, 0)), (2, (0, 1, 0)), (3, (1, 0, 0)), (0, (1, 1, 0)),
+                                # column-major C: no operand swap, narrow staged-epilogue tiles on 32..128-row slabs
+                                (1, (0, 1, 1)), (2, (1, 0, 1)), (3, (0, 0, 1))]:
         if lb == 0 and N % 8:
             continue
         bf16 = types >= 2

@@ -139,9 +139,10 @@ def test_launch_plan_rules():
     assert p.kernel == 3 and p.tile_m in (64, 128)
     # K not a multiple of 64: one k-block per slot (plain 3-D maps)
     assert g.plan(16, 8192, 8200, 0, 0, 1, types=1, sm_count=148).k_blocks_per_slot == 1
-    # column-major C of a skinny problem: the narrow staged-epilogue variant, no operand swap
+    # column-major C of a skinny problem: the narrow staged-epilogue variant, no operand swap,
+    # slabs in whole 32-row store groups (128 slabs of 64 rows, K not partitioned)
     p = g.plan(16, 8192, 8192, 1, 0, 1, types=1, sm_count=148)
-    assert (p.kernel, p.tile_m, p.tile_n, p.cluster) == (2, 128, 16, 1)
+    assert (p.kernel, p.tile_m, p.tile_n, p.cluster, p.split_k, p.ctas) == (2, 64, 16, 1, 1, 128)
     # the headline size runs on CTA pairs, one k-block per slot, every SM busy
     p = g.plan(8192, 8192, 8192, 0, 0, 1, types=3, sm_count=148)
     assert (p.kernel, p.cluster, p.tile_m, p.k_blocks_per_slot, p.ctas) == (2, 2, 256, 1, 148) and p.tile_n in (256, 512)

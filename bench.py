@@ -39,7 +39,7 @@ LAYOUT_NAMES = ["".join("rc"[x] for x in l) for l in LAYOUTS]
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # DRAM bytes (read + write) of one 8192^3 bf16->f32 launch of gemm_umma_kernel, from the ncu
 # capture summarised in profiles/.
-NCU_DRAM_BYTES_PER_LAUNCH_8192 = 1.19e9  # mean of the three captured launches (1.37, 1.10, 1.10 GB; profiles/gemm_umma_8192cubed_bf16_f32.md)
+NCU_DRAM_BYTES_PER_LAUNCH_8192 = 1.19e9  # mean of the three captured launches: 1.37, 1.10 and 1.10 GB
 
 
 def load_peaks():

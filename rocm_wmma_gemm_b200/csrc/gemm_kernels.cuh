@@ -274,17 +274,22 @@ __device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits)
 // both CTAs' shared memory and writes both CTAs' TMEM (each holds its 128 rows x BN columns).
 // The pair halves the B' bytes each SM has to stage per FLOP.
 //
-//   warp 0 (one lane)  TMA producer: fills a `stages`-deep ring of {A' 128x64, B' (BN/CL)x64}
-//                      tiles (128-byte swizzle).  Slot s has a `full` barrier (bytes landed;
-//                      for a pair it lives in rank 0 and counts both CTAs' bytes) and an
-//                      `empty` barrier (MMAs that read the slot have retired).
-//   warp 1 (one lane)  MMA issuer (rank 0 only for a pair): 4 x tcgen05.mma per slot into one
-//                      of the TMEM accumulators (BN f32 columns each); tcgen05.commit releases
-//                      the slot and, after the last k-block, publishes the accumulator.
+//   warp 0 (one elected lane)  TMA producer: fills a `stages`-deep ring of slots (128-byte
+//                      swizzle): {A' 128x64, B' (BN/CL)x64} per slot, or - one-CTA kernels up to
+//                      256 columns - kc k-blocks of {A' bm x 64, B' BN x 64}, one TMA instruction
+//                      per operand.  Slot s has a `full` barrier (bytes landed; for a pair it
+//                      lives in rank 0 and counts both CTAs' bytes) and an `empty` barrier
+//                      (MMAs that read the slot have retired).
+//   warp 1 (one elected lane)  MMA issuer (rank 0 only for a pair): 4 x tcgen05.mma per
+//                      k-block into one of the TMEM accumulators (BN f32 columns each);
+//                      tcgen05.commit releases the slot and, after the last k-block, publishes
+//                      the accumulator.  (The two single threads are chosen with elect.sync:
+//                      the compiler then issues TMA / MMA / commit from uniform registers.)
 //   warps 2..5         epilogue: tcgen05.ld 32 lanes x 32 columns, convert, swizzled store to a
 //                      per-warp staging buffer, TMA store of 32 rows x 128 B; the accumulator
 //                      is handed back as soon as its last column chunk is in registers, so the
-//                      epilogue of tile i overlaps the main loop of tile i + 1.
+//                      epilogue of tile i overlaps the main loop of tile i + 1.  TR = true:
+//                      the transposing epilogue of skinny problems (direct coalesced stores).
 //
 // Edges: TMA zero-fills out-of-range loads (M, N and K tails) and clips stores.
 // No TMA load here uses cluster multicast.

@@ -42,7 +42,7 @@ from rocm_wmma_gemm_b200.config.gomea import INF, Gomea  # noqa: E402
 PARAMS = ["tile_m", "tile_n", "stages", "split_k", "raster"]
 SPACE = {
     "tile_m": [128, 256],
-    "tile_n": [64, 128, 256, 512],
+    "tile_n": [64, 128, 160, 192, 224, 256, 512],   # 160 / 192 / 224: run-time widths of the 256-column pair kernel
     "stages": [2, 3, 4, 6, 8, 12],
     "split_k": [1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 12, 14, 16, 24, 32],
     "raster": [0, 1, 2, 4, 8, 16, 32],
@@ -71,8 +71,12 @@ def cluster_of(tile_m: int) -> int:
     return tile_m // 128
 
 
+def compiled_width(tile_n: int) -> int:
+    return tile_n if tile_n <= 64 else 128 if tile_n <= 128 else 256 if tile_n <= 256 else 512
+
+
 def stage_bytes(tile_n: int, cluster: int) -> int:
-    return 128 * 64 * 2 + (tile_n // cluster) * 64 * 2
+    return 128 * 64 * 2 + (compiled_width(tile_n) // cluster) * 64 * 2
 
 
 def max_stages(tile_n: int, cluster: int) -> int:
@@ -85,6 +89,8 @@ def check_constraints(cfg, M=None, N=None, K=None, lc=0) -> bool:
     cl = cluster_of(tile_m)
     if cl == 1 and tile_n > 256:
         return False                      # one CTA holds two accumulators: 2 * tile_n <= 512 TMEM columns
+    if tile_n != compiled_width(tile_n) and cl != 2:
+        return False                      # in-between widths exist for CTA pairs only
     if cl == 2 and tile_n < 128:
         return False                      # each CTA of a pair stages >= 64 rows of B
     if stages > max_stages(tile_n, cl):

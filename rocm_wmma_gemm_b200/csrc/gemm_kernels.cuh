@@ -53,6 +53,7 @@ struct GemmParams {
     uint32_t k_skew;       // work unit w starts its K loop (w * k_skew) k-blocks in (0 = in order)
     uint32_t stagger;      // 512-wide tiles: k-blocks by which the two column halves are staggered
     uint32_t bm;           // one-CTA kernels: rows of A' per tile (128; 8 .. 128 with the transposed epilogue)
+    uint32_t wn;           // CTA-pair kernels up to 256 columns: columns per tile actually used (<= BN)
     uint32_t kc;           // one-CTA kernels: k-blocks per ring slot (1, 2 or 4)
     uint32_t k4d;          // one-CTA kernels: K-major operands use the 4-D (chunked K) maps
 };
@@ -353,6 +354,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     const uint32_t a_bytes = SLOT ? p.bm * (BLOCK_K * 2u) : A_TILE_BYTES;
     const uint32_t pitch   = SLOT ? kc * (a_bytes + B_TILE_BYTES) : STAGE_BYTES;
     const uint32_t tile_m  = SLOT ? p.bm : static_cast<uint32_t>(BLOCK_M * CL);
+    // CTA-pair kernels up to 256 columns take the tile width at run time (any multiple of the
+    // epilogue's 128-byte chunk up to BN): the MMA's N extent is a field of the instruction
+    // descriptor and the B' box height a field of the tensor map, so one compiled kernel serves
+    // widths that cut N into whole waves of tiles.  Ring slots and TMEM stay sized for BN.
+    constexpr bool FLEX     = (CL == 2) && (NSUB == 1);
+    const uint32_t wn       = FLEX ? p.wn : static_cast<uint32_t>(BN);
+    const uint32_t sub_rows = FLEX ? wn / CL : static_cast<uint32_t>(SUB_ROWS);
+    const uint32_t sub_bytes = FLEX ? sub_rows * (BLOCK_K * 2u) : SUB_BYTES;
 
     const uint32_t ring = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u; // ring of operand tiles
     const uint32_t epi  = ring + stages * pitch;                      // epilogue staging (unused when TR)
@@ -398,9 +407,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             uint32_t stage = 0, phase = 0, issued = 0;
             bool     ok = true;
             for (uint32_t w = unit; ok && w < p.num_work; w += units) {
-                const WorkCoord c  = decode_work(p, w, BN, tile_m);
+                const WorkCoord c  = decode_work(p, w, wn, tile_m);
                 const int32_t   am = static_cast<int32_t>(c.m0 + rank * BLOCK_M);
-                const int32_t   bn = static_cast<int32_t>(c.n0 + rank * SUB_ROWS);
+                const int32_t   bn = static_cast<int32_t>(c.n0 + rank * sub_rows);
                 // Streaming (HBM-bound) problems rotate each work unit's K order so that the CTAs
                 // running at the same time read different K offsets: rows of a K-major operand
                 // are a power of two apart, and same-offset reads from thousands of rows land on
@@ -461,7 +470,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     const uint32_t sa = ring + stage * pitch;
                     const uint32_t sb = sa + a_bytes;
                     const int32_t  k0 = static_cast<int32_t>(kb * BLOCK_K);
-                    const uint32_t step_bytes = a_bytes + nsub * SUB_BYTES; // this CTA's share
+                    const uint32_t step_bytes = a_bytes + nsub * sub_bytes; // this CTA's share
                     uint32_t       bar = ptx::smem_u32(&s_full[stage]);
                     if constexpr (CL == 2) {
                         // Rank 0 owns the pair's full barrier and expects both CTAs' bytes.
@@ -488,8 +497,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                         } else {
 #pragma unroll
                             for (int j = 0; j < SUB_ROWS / 64; ++j)
-                                tma_load<CL>(sh + j * (64 * BLOCK_K * 2), &tmB, bar, bh + j * 64,
-                                             k0, c.z_in);
+                                if (!FLEX || static_cast<uint32_t>(j) * 64u < sub_rows)
+                                    tma_load<CL>(sh + j * (64 * BLOCK_K * 2), &tmB, bar, bh + j * 64,
+                                                 k0, c.z_in);
                         }
                     }
                     ++issued;
@@ -530,7 +540,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             uint32_t       stage = 0, phase = 0, it = 0;
             bool           ok = true;
             for (uint32_t w = unit; ok && w < p.num_work; w += units, ++it) {
-                const WorkCoord c = decode_work(p, w, BN, tile_m);
+                const WorkCoord c = decode_work(p, w, wn, tile_m);
                 if constexpr (NSUB == 2) {
                     // Two column halves with their own full / empty barriers (s_tfull[h],
                     // s_tempty[h]), staggered by stg_x k-blocks: see TileStep.  Three
@@ -670,7 +680,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         uint32_t       it   = 0, nstore = 0;
         bool           ok   = true;
         for (uint32_t w = unit; ok && w < p.num_work; w += units, ++it) {
-            const WorkCoord c      = decode_work(p, w, BN, tile_m);
+            const WorkCoord c      = decode_work(p, w, wn, tile_m);
             const uint32_t  buf    = it % NUM_ACC;
             const uint32_t  aphase = (it / NUM_ACC) & 1u;
             // A 512-wide tile is drained as two 256-column halves, each published (s_tfull[h])
@@ -734,7 +744,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
             uint32_t       n0[32], n1[32]; // raw accumulator words of the chunk in flight
             ptx::tmem_ld_32x32(tacc, n0);
             if constexpr (OUT != OUT_F32) ptx::tmem_ld_32x32(tacc + 32u, n1);
-            constexpr int NCH_H = NCHUNK / NSUB; // chunks per half
+            const int NCH_H = FLEX ? static_cast<int>(wn) / CH : NCHUNK / NSUB; // chunks per half
 #pragma unroll 1
             for (int ch = 0; ch < NCH_H; ++ch) {
                 uint32_t v[32];

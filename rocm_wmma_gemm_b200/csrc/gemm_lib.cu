@@ -398,13 +398,22 @@ static bool tma_ok(const Problem& p, const View& v)
 // ------------------------------------------------------------------------------------------
 // Configuration handling
 // ------------------------------------------------------------------------------------------
+// The compiled kernel width that serves a tile width (see check_config).
+static inline int compiled_width(int tile_n)
+{
+    return tile_n <= 64 ? tile_n : (tile_n <= 128 ? 128 : (tile_n <= 256 ? 256 : 512));
+}
+
 static int check_config(const b200_gemm_config& c)
 {
     if (c.cluster != 1 && c.cluster != 2) return fail(B200_GEMM_ERR_BAD_CONFIG, "cluster %d not compiled (1 or 2)", c.cluster);
     if (c.tile_m != 128 * c.cluster)
         return fail(B200_GEMM_ERR_BAD_CONFIG, "tile_m %d does not match cluster %d (tile_m = 128 * cluster)", c.tile_m, c.cluster);
-    if (c.tile_n != 64 && c.tile_n != 128 && c.tile_n != 256 && c.tile_n != 512)
-        return fail(B200_GEMM_ERR_BAD_CONFIG, "tile_n %d not compiled (64, 128, 256, 512)", c.tile_n);
+    // CTA-pair kernels take any width between 128 and 256 columns that is a multiple of 32
+    // (run-time field of the 256-column kernel); everything else is a compiled width.
+    const bool flex_width = c.cluster == 2 && c.tile_n > 128 && c.tile_n < 256 && c.tile_n % 32 == 0;
+    if (!flex_width && c.tile_n != 64 && c.tile_n != 128 && c.tile_n != 256 && c.tile_n != 512)
+        return fail(B200_GEMM_ERR_BAD_CONFIG, "tile_n %d not available (64, 128, 256, 512; with cluster 2 also 160, 192, 224)", c.tile_n);
     if (c.cluster == 2 && c.tile_n == 64) return fail(B200_GEMM_ERR_BAD_CONFIG, "tile_n 64 needs cluster 1");
     if (c.cluster == 1 && c.tile_n == 512) return fail(B200_GEMM_ERR_BAD_CONFIG, "tile_n 512 needs cluster 2");
     if (c.stages < 2 || c.stages > MAX_STAGES) return fail(B200_GEMM_ERR_BAD_CONFIG, "stages %d outside 2..%d", c.stages, MAX_STAGES);
@@ -417,7 +426,7 @@ static int check_config(const b200_gemm_config& c)
 // holds and give every K partition at least one k-block.
 static void legalize(b200_gemm_config& c, const View& v, uint32_t* kb_per_split)
 {
-    const int ms = max_stages(c.tile_n, c.cluster);
+    const int ms = max_stages(compiled_width(c.tile_n), c.cluster);
     if (c.stages > ms) c.stages = ms;
     const uint32_t k_blocks = (v.K + BLOCK_K - 1) / BLOCK_K;
     uint32_t       split    = (uint32_t)c.split_k;
@@ -724,6 +733,17 @@ static int make_plan(const Problem& p, const b200_gemm_config* user_cfg, int sm_
         cfg.tile_n  = v.N <= 16 ? 16 : (v.N <= 32 ? 32 : (v.N <= 64 ? 64 : 128));
         if (v.b_mn && cfg.tile_n < 64) cfg.tile_n = 64;
     }
+    // A width between the compiled ones needs a K-major B' (an N-major B' is loaded in 64-row
+    // boxes) and whole 128-byte output chunks (32 f32 or 64 16-bit columns).
+    if (cfg.tile_n != compiled_width(cfg.tile_n)) {
+        const int chunk = out_is_f32(p.types) ? 32 : 64;
+        if (v.b_mn || cfg.tile_n % chunk) {
+            if (user_cfg)
+                return fail(B200_GEMM_ERR_BAD_CONFIG, "tile_n %d needs a K-major B operand in the kernel view and a multiple of %d columns",
+                            cfg.tile_n, chunk);
+            cfg.tile_n = 256; // a borrowed table entry that does not fit this layout / type
+        }
+    }
     // Transposed problems are HBM-bound streams of A' (the caller's large operand).  Its rows are
     // cut into slabs of `bm` <= 128 rows so that the slabs fill whole waves of the SMs: every SM
     // streams the same number of bytes, no K partition and no reduction pass is needed.  (The
@@ -838,6 +858,7 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     gp.batch        = (uint32_t)p.batch;
     const uint32_t cl   = (uint32_t)cfg.cluster;
     gp.bm           = bm;
+    gp.wn           = (uint32_t)cfg.tile_n;
     gp.kc           = kc;
     gp.k4d          = k4d ? 1u : 0u;
     gp.m_tiles      = slot ? (v.M + bm - 1) / bm : (v.M + BLOCK_M * cl - 1) / (BLOCK_M * cl);
@@ -918,7 +939,7 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     }
 
     const uint32_t smem     = transposed ? slab_smem_bytes((int)bm, bn, (int)kc, cfg.stages)
-                              : (slot ? slot_smem_bytes(bn, (int)kc, cfg.stages) : gemm_smem_bytes(bn, (int)cl, cfg.stages));
+                              : (slot ? slot_smem_bytes(bn, (int)kc, cfg.stages) : gemm_smem_bytes(compiled_width(bn), (int)cl, cfg.stages));
     const uint32_t units    = std::min<uint32_t>(gp.num_work, (uint32_t)ctx->sm_count / cl);
     const int      kern_out = split > 1 ? OUT_F32 : out;
     cudaError_t    e;
@@ -930,8 +951,8 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
             default: e = launch_bn<128, 1, true>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
         }
     } else if (cl == 2) {
-        if (bn == 128) e = launch_bn<128, 2>(kern_out, units, &ctx->pair_units[0], smem, stream, tmA, tmB, tmD, gp);
-        else if (bn == 256) e = launch_bn<256, 2>(kern_out, units, &ctx->pair_units[1], smem, stream, tmA, tmB, tmD, gp);
+        if (bn <= 128) e = launch_bn<128, 2>(kern_out, units, &ctx->pair_units[0], smem, stream, tmA, tmB, tmD, gp);
+        else if (bn <= 256) e = launch_bn<256, 2>(kern_out, units, &ctx->pair_units[1], smem, stream, tmA, tmB, tmD, gp);
         else e = launch_bn<512, 2>(kern_out, units, &ctx->pair_units[2], smem, stream, tmA, tmB, tmD, gp);
     } else {
         switch (bn) {
@@ -1061,6 +1082,7 @@ static int run_gemm_static(const Problem& p, cudaStream_t stream, const b200_gem
     b200_gemm_config cfg = resolve_config(p, user_cfg, nullptr);
     st                   = check_config(cfg);
     if (st != B200_GEMM_OK) return st;
+    cfg.tile_n = compiled_width(cfg.tile_n); // this entry point keeps to the compiled tile widths
     uint32_t kb_per_split = 0;
     legalize(cfg, v, &kb_per_split);
 
@@ -1084,6 +1106,7 @@ static int run_gemm_static(const Problem& p, cudaStream_t stream, const b200_gem
     gp.K            = v.K;
     gp.batch        = (uint32_t)p.batch;
     gp.bm           = BLOCK_M;
+    gp.wn           = (uint32_t)cfg.tile_n;
     gp.kc           = 1;
     gp.k4d          = 0;
     gp.m_tiles      = (v.M + BLOCK_M * cl - 1) / (BLOCK_M * cl);

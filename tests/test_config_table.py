@@ -107,6 +107,7 @@ def test_constraints():
     assert ok((128, 256, 4, 1, 8)) and not ok((128, 512, 2, 1, 8))        # 512 columns need a CTA pair
     assert not ok((256, 64, 4, 1, 8))                                      # a pair stages >= 64 B rows per CTA
     assert ok((128, 64, 8, 1, 8)) and ok((256, 128, 8, 1, 8))
+    assert ok((256, 192, 6, 1, 8)) and not ok((128, 192, 4, 1, 8))         # in-between widths: CTA pairs only
     assert not ok((128, 128, 4, 32, 0), 128, 128, 1024)                    # more partitions than k-blocks
     assert not ok((128, 128, 4, 3, 0), 128, 128, 256)                      # 4 k-blocks in 3 parts is really 2
     assert len(tune.enumerate_valid(8192, 8192, 8192, 0)) > 500

@@ -442,3 +442,32 @@ def test_dependent_calls_back_to_back_and_in_a_graph():
     for r, o in zip(ref, gb):
         assert torch.equal(r.view(torch.int16), o.view(torch.int16))
     assert float(ref[4].float().abs().max()) > 0
+
+
+@pytest.mark.parametrize("tile_n", [160, 192, 224])
+def test_pair_tile_widths_between_the_compiled_ones(tile_n):
+    """The 256-column CTA-pair kernel takes its tile width at run time (multiples of 32 columns
+    between 128 and 256; whole 128-byte output chunks, so 16-bit outputs need multiples of 64;
+    the kernel view's B' must be K-major).  Ragged N, split-K and raster bands on top."""
+    M, N, K = 640, 1000 if tile_n != 192 else 1184, 448
+    for types in range(4):
+        bf16 = types >= 2
+        chunk = 32 if types in (1, 3) else 64
+        for (la, lb, lc) in [(0, 1, 0), (1, 1, 0), (0, 0, 1), (0, 1, 1)]:
+            A, B = seeded(M, N, K, la, lb, bf16)
+            for split_k, raster in [(1, 0), (2, 2)]:
+                cfg = g.GemmConfig(256, tile_n, 6, 2, split_k, raster)
+                if tile_n % chunk:
+                    with pytest.raises(g.GemmError):
+                        gpu_gemm(types, A, B, M, N, K, lc, la, lb, config=cfg)
+                    continue
+                ref = oracle.hgemm(types, A, B, M, N, K, lc, la, lb)
+                got = gpu_gemm(types, A, B, M, N, K, lc, la, lb, config=cfg)
+                check_parity(types, got, ref, K, SIGMA_UNIFORM, M, N, lc)
+    # an N-major B' (row-major B with a row-major C) cannot use an in-between width
+    A, B = seeded(M, N, K, 0, 0, True)
+    with pytest.raises(g.GemmError):
+        gpu_gemm(3, A, B, M, N, K, 0, 0, 0, config=g.GemmConfig(256, tile_n, 6, 2, 1, 0))
+    # ... and one CTA cannot either
+    with pytest.raises(g.GemmError):
+        gpu_gemm(3, A, B, M, N, K, 0, 0, 1, config=g.GemmConfig(128, tile_n, 4, 1, 1, 0))

@@ -91,8 +91,12 @@ enum b200_gemm_types {
  * (rocm_wmma_gemm/config/gemm_config_gfx1100_f16.json:1-22; struct gemm_params generated by
  * rocm_wmma_gemm/config/generate_config.py:94-103).
  *   tile_m   rows of C per CTA (per CTA pair when cluster == 2): 128, or 256 with cluster 2
- *   tile_n   columns of C per CTA / CTA pair: 64, 128, 256, or 512 (512: cluster 2 only)
- *   stages   depth of the TMA -> shared-memory ring (2 .. 8, clamped to what fits)
+ *   tile_n   columns of C per CTA / CTA pair: 64, 128, 256, or 512 (512: cluster 2 only); with
+ *            cluster 2 also 160, 192 and 224 (the 256-column kernel at a run-time width; needs
+ *            a K-major B operand in the kernel view and whole 128-byte output chunks, i.e. a
+ *            multiple of 32 columns for f32 outputs, of 64 for 16-bit outputs)
+ *   stages   depth of the TMA -> shared-memory ring (2 .. 12, clamped to what fits; kernels
+ *            that stage several k-blocks per ring slot size the ring themselves)
  *   cluster  1 = one CTA per tile, 2 = a CTA pair shares one tile (cta_group::2 MMA)
  *   split_k  number of K partitions reduced through an f32 workspace (1 = none)
  *   raster   tile-rows per raster band (the reference's `swizzle` key); 0 = column sweep

@@ -283,8 +283,10 @@ def test_skinny_shapes(M, N, K):
                 check_parity(types, got, ref, K, SIGMA_UNIFORM, M, N, lc)
 
 
-def test_skinny_batched():
-    M, N, K, batch = 16, 512, 256, 3
+@pytest.mark.parametrize("M,N,K,batch", [(16, 512, 256, 3), (16, 2048, 256, 3), (24, 4104, 192, 2)])
+def test_skinny_batched(M, N, K, batch):
+    """Strided-batched skinny problems; the wider ones are cut into row slabs counted over the
+    whole batch (48-row slabs x 3 matrices fill one wave)."""
     for types in (1, 2):
         bf16 = types >= 2
         for (la, lb, lc) in [(0, 1, 0), (0, 0, 0), (1, 0, 1)]:

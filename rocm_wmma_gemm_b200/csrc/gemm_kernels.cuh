@@ -634,29 +634,27 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                             phase ^= 1u;
                         }
                     }
-                    if (!ok) break;
-                    umma_arrive<CL>(ptx::smem_u32(&s_tfull[buf])); // accumulator complete
-                    continue;
-                }
-                for (uint32_t kb = c.kb0; kb < c.kb1; ++kb) {
-                    ok = bounded_wait(ptx::smem_u32(&s_full[stage]), phase, &s_abort, p.status,
-                                      ST_MMA_WAIT_FULL);
-                    if (!ok) break;
-                    ptx::tc_fence_after();
-                    const uint32_t sa = ring + stage * pitch;
-                    const uint32_t sb = sa + a_bytes;
-                    const uint64_t ad = ptx::make_smem_desc(sa, a_lbo, 1024u);
-                    const uint64_t bd = ptx::make_smem_desc(sb, b_lbo, 1024u);
+                } else {
+                    for (uint32_t kb = c.kb0; kb < c.kb1; ++kb) {
+                        ok = bounded_wait(ptx::smem_u32(&s_full[stage]), phase, &s_abort, p.status,
+                                          ST_MMA_WAIT_FULL);
+                        if (!ok) break;
+                        ptx::tc_fence_after();
+                        const uint32_t sa = ring + stage * pitch;
+                        const uint32_t sb = sa + a_bytes;
+                        const uint64_t ad = ptx::make_smem_desc(sa, a_lbo, 1024u);
+                        const uint64_t bd = ptx::make_smem_desc(sb, b_lbo, 1024u);
 #pragma unroll
-                    for (uint32_t k = 0; k < BLOCK_K / UMMA_K; ++k) {
-                        ptx::umma_f16<CL>(d_tmem, ad + k * a_kstep, bd + k * b_kstep, p.idesc,
-                                          (kb > c.kb0 || k > 0u) ? 1u : 0u);
-                    }
-                    // Slot free (in both CTAs of a pair) once these MMAs retire.
-                    umma_arrive<CL>(ptx::smem_u32(&s_empty[stage]));
-                    if (++stage == stages) {
-                        stage = 0;
-                        phase ^= 1u;
+                        for (uint32_t k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                            ptx::umma_f16<CL>(d_tmem, ad + k * a_kstep, bd + k * b_kstep, p.idesc,
+                                              (kb > c.kb0 || k > 0u) ? 1u : 0u);
+                        }
+                        // Slot free (in both CTAs of a pair) once these MMAs retire.
+                        umma_arrive<CL>(ptx::smem_u32(&s_empty[stage]));
+                        if (++stage == stages) {
+                            stage = 0;
+                            phase ^= 1u;
+                        }
                     }
                 }
                 if (!ok) break;

@@ -1336,17 +1336,19 @@ extern "C" int b200_gemm_host(int types, void* C, const void* A, const void* B, 
     // Large single problems are pipelined in two dimensions: A goes up in chunks of rows, B in
     // chunks of columns, alternately; a tile of C is computed as soon as its row chunk and its
     // column chunk are on the device and goes down while later chunks still come up (PCIe is
-    // full duplex).  The first tile starts after 1/8 of A and 1/8 of B.  (Cutting the last
-    // chunks finer, so that fewer tiles are left once the uploads end, was measured slower.)
-    // Chunks and tiles are stored densely on the device, so every tile is an ordinary dense
-    // GEMM whatever the layouts; strided sides are host-side 2-D copies.
+    // full duplex).  Four chunks per dimension: the download of a tile is a strided 2-D copy
+    // whose rate grows with the length of its contiguous runs (timed with events per copy on
+    // 8192^3 f32: 1024-column tiles come down at 28-36 GB/s, the link does 44 GB/s each way),
+    // so fewer, wider tiles win over an earlier start: 8 x 8 chunks 7.75 ms per GEMM, 8 x 4
+    // 7.3, 4 x 4 7.15, 16 x 8 8.2.  Chunks and tiles are stored densely on the device, so every
+    // tile is an ordinary dense GEMM whatever the layouts; strided sides are host-side 2-D copies.
     auto chunk_starts = [](size_t dim) { // chunk boundaries, multiples of 256 (last one = dim)
         std::vector<size_t> b{0};
         if (dim < 2048) {
             b.push_back(dim);
             return b;
         }
-        const size_t step = ((dim + 7) / 8 + 255) / 256 * 256;
+        const size_t step = ((dim + 3) / 4 + 255) / 256 * 256;
         size_t       at   = 0;
         while (dim - at > step) b.push_back(at += step);
         b.push_back(dim);

@@ -42,7 +42,9 @@ enum b200_gemm_status {
     B200_GEMM_ERR_CUDA         = 6, /* a CUDA runtime/driver call failed; see last_error */
     B200_GEMM_ERR_BAD_CONFIG   = 7, /* explicit config outside the compiled variant set */
     B200_GEMM_ERR_DEVICE_WAIT  = 8, /* a kernel gave up on a bounded wait (device status) */
-    B200_GEMM_ERR_TOO_LARGE    = 9  /* request exceeds a fixed-capacity entry point's limit */
+    B200_GEMM_ERR_TOO_LARGE    = 9, /* request exceeds a fixed-capacity entry point's limit */
+    B200_GEMM_ERR_NO_NCCL      = 10, /* the multi-GPU driver could not load libnccl.so.2 */
+    B200_GEMM_ERR_NCCL         = 11  /* an NCCL call failed; see last_error */
 };
 
 /* ---- group 1: the reference's C ABI ----------------------------------------------------
@@ -99,8 +101,13 @@ enum b200_gemm_types {
  *            that stage several k-blocks per ring slot size the ring themselves)
  *   cluster  1 = one CTA per tile, 2 = a CTA pair shares one tile (cta_group::2 MMA)
  *   split_k  number of K partitions reduced through an f32 workspace (1 = none)
- *   raster   tile-rows per raster band (the reference's `swizzle` key); 0 = column sweep
+ *   raster   tile-rows per raster band (the reference's `swizzle` key,
+ *            rocm_wmma_gemm/include/rocm_wmma_gemm/kernel/mapping.hpp:108-287); 0 = column sweep.
+ *            Adding B200_GEMM_RASTER_SNAKE selects the boustrophedon order of the reference's
+ *            xor_snake mappings: every other band walks its columns backwards, so a band starts
+ *            on the panels of B the band before it has just read.
  */
+#define B200_GEMM_RASTER_SNAKE 128
 typedef struct b200_gemm_config {
     int tile_m;
     int tile_n;
@@ -158,8 +165,10 @@ int b200_gemm_plan(int types, size_t M, size_t N, size_t K, size_t batch_count, 
 /* Host-buffer call: A, B, C are HOST pointers (pageable or pinned).  Copies A and B to the
  * device, runs the GEMM, copies C back and synchronises; device buffers are cached per
  * device and grow on demand.  This is the path a caller without device memory of its own
- * uses, and the one the end-to-end benchmark times.  No reference counterpart (the
- * reference's tests do the copies themselves, test/gemm/test_float_accum.cpp:95-119). */
+ * uses, and the one the end-to-end benchmark times.  Calls on the same device are serialised
+ * (the staging buffers and copy streams are per device): a second thread's call waits for the
+ * first to return.  No reference counterpart (the reference's tests do the copies themselves,
+ * test/gemm/test_float_accum.cpp:95-119). */
 int b200_gemm_host(int types, void* C, const void* A, const void* B, size_t M, size_t N, size_t K,
                    size_t batch_count, int layout_c, int layout_a, int layout_b);
 
@@ -167,6 +176,77 @@ int b200_gemm_host(int types, void* C, const void* A, const void* B, size_t M, s
  * owns columns [*n_begin, *n_begin + *n_count) of B and C.  Slab widths are multiples of
  * `align` columns except the last.  No reference counterpart (the reference is single-GPU). */
 int b200_gemm_slab(size_t N, int world, int rank, size_t align, size_t* n_begin, size_t* n_count);
+
+/* ---- multi-GPU column-slab driver ----------------------------------------------------------
+ * C = A*B over `world` GPUs of one box, one host process (or thread) per GPU: A replicated,
+ * GPU `rank` owns the columns b200_gemm_slab assigns it of B and C.  The slab GEMM itself is the
+ * ordinary single-GPU call on (A, B slab, C slab) and needs nothing from this section; what is
+ * here is the exchange around it.  None of it has a counterpart in the reference, which is a
+ * single-GPU library.  NCCL is loaded at run time (libnccl.so.2 on the loader path), so programs
+ * that never create a communicator do not need it.
+ *
+ * Communicator: rank 0 obtains an id (b200_gemm_comm_id), the caller hands the 128 bytes to the
+ * other ranks by whatever channel it has, every rank calls b200_gemm_comm_create with its
+ * device current.  b200_gemm_comm_barrier enqueues a 4-byte all-reduce on `*stream`: work queued
+ * after it starts only when every rank's stream has reached its barrier.
+ * b200_gemm_comm_allgather_inplace all-gathers `bytes_per_rank` bytes per rank inside `buf`
+ * (rank r's block at buf + r * bytes_per_rank already holds its own data): with row-major A cut
+ * into `world` row blocks, each GPU uploads one block from the host and NVLink carries the rest. */
+#define B200_GEMM_COMM_ID_BYTES 128
+#define B200_GEMM_IPC_HANDLE_BYTES 64
+typedef struct b200_gemm_comm b200_gemm_comm;
+int b200_gemm_comm_id(void* id /* B200_GEMM_COMM_ID_BYTES out */);
+int b200_gemm_comm_create(const void* id, int world, int rank, b200_gemm_comm** out);
+int b200_gemm_comm_destroy(b200_gemm_comm* comm);
+int b200_gemm_comm_barrier(b200_gemm_comm* comm, void* stream);
+int b200_gemm_comm_allgather_inplace(b200_gemm_comm* comm, void* buf, size_t bytes_per_rank, void* stream);
+
+/* Device memory other processes of the box can map: b200_gemm_peer_alloc allocates on the
+ * current device and fills `handle` (B200_GEMM_IPC_HANDLE_BYTES, to be sent to the other
+ * processes); b200_gemm_peer_open maps a buffer another process allocated and returns its
+ * address in this process (valid on the current device; peer access is enabled on demand).
+ * Close every mapping before the owner frees the buffer. */
+int b200_gemm_peer_alloc(size_t bytes, void** dptr, void* handle);
+int b200_gemm_peer_open(const void* handle, void** dptr);
+int b200_gemm_peer_close(void* dptr);
+int b200_gemm_peer_free(void* dptr);
+
+/* The optional gather of C, three ways.  All leave the full M x N matrix (layout_c) on every
+ * GPU; slabs are those of b200_gemm_slab(N, world, rank, align); `types` picks the element size
+ * of C.
+ *
+ * b200_gemm_slab_allgather: NCCL all-gather of the C slabs (slab = dense M x n_count matrix in
+ *   layout_c).  Column-major slabs land in place.  Row-major slabs interleave row by row: they
+ *   are gathered into `staging` (M x N elements, caller-owned) and a re-layout kernel writes
+ *   C_full.  Unequal slabs (N not a multiple of world x align) go as one grouped broadcast per
+ *   slab.
+ * b200_gemm_slab_push: this GPU's slab is copied into C_full[d] of every GPU d (C_full[rank] is
+ *   local, the others are peer mappings) by the copy engines: strided device-to-device copies,
+ *   no staging, no kernel, no SM taken from a GEMM that runs beside them.  The matrices are
+ *   complete once every rank's copies have finished (b200_gemm_comm_barrier).
+ * b200_gemm_slab_gather: the slab GEMM with the gather fused into its epilogue: every tile of
+ *   the slab is stored straight into C_full[d] of all GPUs while the next tile is computed, so
+ *   the exchange rides under the GEMM and there is no slab buffer at all.  Runs on the
+ *   256 x 256 / 256 x 512 CTA-pair tiles (cfg NULL: the table's entry, moved onto one of them if
+ *   needed) without K partitions; slab boundaries must be multiples of 64 columns (align 64 or
+ *   a multiple).  C_full complete once every rank's kernel has finished
+ *   (b200_gemm_comm_barrier). */
+int b200_gemm_slab_allgather(b200_gemm_comm* comm, int types, void* C_full, const void* C_slab, void* staging,
+                             size_t M, size_t N, int layout_c, size_t align, void* stream);
+int b200_gemm_slab_push(int types, void* const* C_full, const void* C_slab, size_t M, size_t N, int layout_c,
+                        int world, int rank, size_t align, void* stream);
+int b200_gemm_slab_gather(int types, void* const* C_full, const void* A, const void* B_slab, size_t M, size_t N,
+                          size_t K, int layout_c, int layout_a, int layout_b, int world, int rank, size_t align,
+                          void* stream, const b200_gemm_config* cfg);
+
+/* Host-buffer slab call, the multi-GPU counterpart of b200_gemm_host: every rank passes the
+ * whole A (host memory, the same matrix on every rank), its own dense B slab (K x n_count,
+ * layout_b) and room for its own dense C slab (M x n_count, layout_c); pointers may be pageable
+ * or pinned.  Each GPU uploads only 1/world of A's storage over PCIe; an in-place NCCL all-gather
+ * over NVLink completes the replica while the B slab comes up.  Collective: every rank of the
+ * communicator must call it with the same M, N, K, layouts and align.  Synchronous. */
+int b200_gemm_slab_host(b200_gemm_comm* comm, int types, void* C_slab, const void* A, const void* B_slab, size_t M,
+                        size_t N, size_t K, int layout_c, int layout_a, int layout_b, size_t align);
 
 /* Bytes of f32 split-K workspace a call would use (0 when the chosen config has split_k 1). */
 size_t b200_gemm_workspace_bytes(int types, size_t M, size_t N, size_t K, size_t batch_count,
@@ -194,13 +274,21 @@ size_t b200_gemm_workspace_bytes(int types, size_t M, size_t N, size_t K, size_t
  *     left there.  Nothing in it needs to start at zero (every partial is fully overwritten
  *     before it is read), but two calls that overlap on the GPU — different streams, or
  *     different threads — race on it: serialise them on one stream or with events.
- *   - Failures of device-side waits are recorded in a status word of this entry point's own,
- *     not the one b200_gemm_device_status reads.
+ *   - Failures of device-side waits are recorded in a status word of this entry point's own
+ *     (also part of the library image); read it with b200_gemm_static_status.
+ *   - Planning and launch are those of b200_gemm_ex (same kernels, tiles, operand swap for
+ *     skinny problems, raster); only the sources of the workspace and the status word differ.
  * cfg == NULL lets the tuned table choose.  This entry point has no counterpart in the
  * reference library, which never uses scratch memory. */
 int b200_gemm_splitk_static(int types, void* C, const void* A, const void* B, size_t M, size_t N,
                             size_t K, size_t batch_count, int layout_c, int layout_a, int layout_b,
                             void* stream, const b200_gemm_config* cfg);
+
+/* b200_gemm_device_status for the kernels launched by b200_gemm_splitk_static: synchronises
+ * the current device, reads that entry point's own status word (a plain copy from the library
+ * image: nothing is allocated), returns B200_GEMM_ERR_DEVICE_WAIT and clears the word if a
+ * kernel gave up on a bounded wait.  No reference counterpart. */
+int b200_gemm_static_status(unsigned int* detail);
 
 /* Synchronises the current device and returns B200_GEMM_ERR_DEVICE_WAIT if any kernel of
  * this library has given up on a bounded wait since the last call (then clears the flag),

@@ -20,6 +20,7 @@ DEPENDS = SOURCES + [
     os.path.join(PKG_DIR, "csrc", "gemm_kernels.cuh"),
     os.path.join(PKG_DIR, "csrc", "ptx_sm100.cuh"),
     os.path.join(PKG_DIR, "csrc", "config_table.inc"),
+    os.path.join(PKG_DIR, "csrc", "slab_driver.inc"),
     os.path.join(ROOT_DIR, "include", "b200_gemm.h"),
 ]
 
@@ -49,7 +50,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     """Compile the library if it is missing or older than its sources; returns its path."""
     if not force and not is_stale():
         return LIB_PATH
-    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB_PATH] + SOURCES
+    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB_PATH] + SOURCES + ["-ldl"]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if verbose:
         sys.stderr.write(proc.stderr)

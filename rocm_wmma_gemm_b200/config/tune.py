@@ -45,8 +45,10 @@ SPACE = {
     "tile_n": [64, 128, 160, 192, 224, 256, 512],   # 160 / 192 / 224: run-time widths of the 256-column pair kernel
     "stages": [2, 3, 4, 6, 8, 12],
     "split_k": [1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 12, 14, 16, 24, 32],
-    "raster": [0, 1, 2, 4, 8, 16, 32],
+    # band height in tile-rows (0 = column sweep); + RASTER_SNAKE: every other band backwards
+    "raster": [0, 1, 2, 4, 8, 16, 32, 128, 130, 132, 136, 144, 160],
 }
+RASTER_SNAKE = 128  # B200_GEMM_RASTER_SNAKE of include/b200_gemm.h
 SMEM_LIMIT = 232448          # bytes a CTA may use
 EPILOGUE_BYTES = 4 * 2 * 4096  # per-warp double-buffered store staging
 WORKSPACE_LIMIT = 4 << 30    # split-K partials the tuner is willing to allocate
@@ -107,8 +109,11 @@ def check_constraints(cfg, M=None, N=None, K=None, lc=0) -> bool:
     if M is not None:
         mk, nk = (M, N) if lc == 0 else (N, M)   # kernel view: column-major C swaps the roles
         m_tiles = -(-mk // tile_m)
-        if raster > max(1, m_tiles) and raster not in (0, 1):
+        band = raster & ~RASTER_SNAKE
+        if band > max(1, m_tiles) and band not in (0, 1):
             return False                  # bands taller than the matrix are all the same sweep
+        if raster & RASTER_SNAKE and m_tiles * (-(-nk // tile_n)) < 8:
+            return False                  # a handful of tiles: every order is the same wave
     return True
 
 

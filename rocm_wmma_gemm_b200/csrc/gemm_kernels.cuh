@@ -56,7 +56,22 @@ struct GemmParams {
     uint32_t wn;           // CTA-pair kernels up to 256 columns: columns per tile actually used (<= BN)
     uint32_t kc;           // one-CTA kernels: k-blocks per ring slot (1, 2 or 4)
     uint32_t k4d;          // one-CTA kernels: K-major operands use the 4-D (chunked K) maps
+    uint32_t snake;        // raster: odd bands (odd columns of a column sweep) run backwards
+    uint32_t l2_hints;     // L2 eviction priorities: bits [0,2) A', [2,4) B', [4,6) D (L2_HINT_*)
+    uint32_t ndst;         // gathering kernels: number of destination matrices every tile is stored to
+    uint32_t dst_row0;     // gathering kernels: row and column of D(0, 0) within each destination
+    uint32_t dst_col0;
 };
+
+// Destinations of a gathering kernel: one tensor map per copy of the full output matrix (this
+// GPU's own and its peers'), all of the same shape.
+constexpr int MAX_GATHER_DST = 8;
+struct GatherMaps {
+    CUtensorMap m[MAX_GATHER_DST];
+};
+
+// L2 eviction priority of one operand's TMA traffic (GemmParams::l2_hints).
+enum : uint32_t { L2_HINT_NONE = 0u, L2_HINT_EVICT_FIRST = 1u, L2_HINT_EVICT_LAST = 2u };
 
 constexpr int      BLOCK_M        = 128;
 constexpr int      BLOCK_K        = 64; // 64 x 2 B = one 128-byte swizzle row
@@ -176,17 +191,28 @@ __device__ __forceinline__ WorkCoord decode_work(const GemmParams& p, uint32_t w
     const uint32_t split = r % p.split_k;
     const uint32_t b     = r / p.split_k;
     uint32_t       m_idx, n_idx;
+    // Raster (the reference's tile_mapper, kernel/mapping.hpp:108-287): tiles are walked in bands
+    // of group_m tile-rows, tile-rows fastest, so that the tiles in flight share a panel of A'
+    // and a few panels of B' in L2.  With `snake` every other band runs its columns backwards
+    // (and every other column its rows): the first tiles of a band reuse the B' panels the last
+    // tiles of the band before it have just read.
     if (p.group_m == 0u) {
         m_idx = t % p.m_tiles;
         n_idx = t / p.m_tiles;
+        if (p.snake && (n_idx & 1u)) m_idx = p.m_tiles - 1u - m_idx;
     } else {
         const uint32_t per_group = p.group_m * p.n_tiles;
         const uint32_t g         = t / per_group;
         const uint32_t first_m   = g * p.group_m;
         const uint32_t gsize     = min(p.group_m, p.m_tiles - first_m);
         const uint32_t in_g      = t - g * per_group;
-        m_idx                    = first_m + in_g % gsize;
+        uint32_t       m_in      = in_g % gsize;
         n_idx                    = in_g / gsize;
+        if (p.snake) {
+            if (n_idx & 1u) m_in = gsize - 1u - m_in;
+            if (g & 1u) n_idx = p.n_tiles - 1u - n_idx;
+        }
+        m_idx = first_m + m_in;
     }
     WorkCoord c;
     c.m0    = m_idx * static_cast<uint32_t>(bm);
@@ -210,10 +236,10 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
 // shared::cluster address naming the pair leader's barrier (CL = 2).
 template <int CL>
 __device__ __forceinline__ void tma_load(uint32_t dst, const CUtensorMap* tm, uint32_t bar,
-                                         int32_t c0, int32_t c1, int32_t c2)
+                                         int32_t c0, int32_t c1, int32_t c2, uint64_t policy)
 {
-    if constexpr (CL == 2) ptx::tma_load_3d_pair(dst, tm, bar, c0, c1, c2);
-    else ptx::tma_load_3d(dst, tm, bar, c0, c1, c2);
+    if constexpr (CL == 2) ptx::tma_load_3d_pair(dst, tm, bar, c0, c1, c2, policy);
+    else ptx::tma_load_3d(dst, tm, bar, c0, c1, c2, policy);
 }
 
 // tcgen05.commit arriving on `bar` of this CTA (CL = 1) or of both CTAs of the pair (CL = 2).
@@ -295,12 +321,11 @@ __device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits)
 // Edges: TMA zero-fills out-of-range loads (M, N and K tails) and clips stores.
 // No TMA load here uses cluster multicast.
 // ---------------------------------------------------------------------------------------------
-template <int BN, int OUT, int CL, bool TR = false>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
-    gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA,
-                     const __grid_constant__ CUtensorMap tmB,
-                     const __grid_constant__ CUtensorMap tmD, const GemmParams p)
+template <int BN, int OUT, int CL, bool TR, bool GATHER>
+__device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUtensorMap& tmB,
+                                               const CUtensorMap* tmDs, const GemmParams& p)
 {
+    const CUtensorMap& tmD = tmDs[0];
     static_assert(BN == 16 || BN == 32 || BN == 64 || BN == 128 || BN == 256 || BN == 512,
                   "BN must be 16, 32, 64, 128, 256 or 512");
     static_assert(CL == 1 || CL == 2, "cluster size must be 1 or 2");
@@ -369,7 +394,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
     if (tid == 0) {
         ptx::prefetch_tensormap(&tmA);
         ptx::prefetch_tensormap(&tmB);
-        ptx::prefetch_tensormap(&tmD);
+        if constexpr (GATHER) {
+            for (uint32_t d = 0; d < p.ndst; ++d) ptx::prefetch_tensormap(&tmDs[d]);
+        } else {
+            ptx::prefetch_tensormap(&tmD);
+        }
         for (uint32_t s = 0; s < stages; ++s) {
             ptx::mbar_init(ptx::smem_u32(&s_full[s]), 1);
             ptx::mbar_init(ptx::smem_u32(&s_empty[s]), 1);
@@ -406,6 +435,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         if (ptx::elect_one()) {
             uint32_t stage = 0, phase = 0, issued = 0;
             bool     ok = true;
+            const uint64_t pol_a = ptx::make_l2_policy(p.l2_hints & 3u);
+            const uint64_t pol_b = ptx::make_l2_policy((p.l2_hints >> 2) & 3u);
             for (uint32_t w = unit; ok && w < p.num_work; w += units) {
                 const WorkCoord c  = decode_work(p, w, wn, tile_m);
                 const int32_t   am = static_cast<int32_t>(c.m0 + rank * BLOCK_M);
@@ -434,19 +465,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                         const uint32_t bar = ptx::smem_u32(&s_full[stage]);
                         ptx::mbar_expect_tx(bar, pitch);
                         if (p.a_mn_major == 0u) {
-                            if (p.k4d) ptx::tma_load_4d(sa, &tmA, bar, 0, am, kb, c.z_in);
-                            else ptx::tma_load_3d(sa, &tmA, bar, k0, am, c.z_in);
+                            if (p.k4d) ptx::tma_load_4d(sa, &tmA, bar, 0, am, kb, c.z_in, pol_a);
+                            else ptx::tma_load_3d(sa, &tmA, bar, k0, am, c.z_in, pol_a);
                         } else {
-                            ptx::tma_load_3d(sa, &tmA, bar, am, k0, c.z_in);
-                            if (p.bm > 64u) ptx::tma_load_3d(sa + half, &tmA, bar, am + 64, k0, c.z_in);
+                            ptx::tma_load_3d(sa, &tmA, bar, am, k0, c.z_in, pol_a);
+                            if (p.bm > 64u) ptx::tma_load_3d(sa + half, &tmA, bar, am + 64, k0, c.z_in, pol_a);
                         }
                         if (p.b_mn_major == 0u) {
-                            if (p.k4d) ptx::tma_load_4d(sb, &tmB, bar, 0, bn, kb, c.z_in);
-                            else ptx::tma_load_3d(sb, &tmB, bar, k0, bn, c.z_in);
+                            if (p.k4d) ptx::tma_load_4d(sb, &tmB, bar, 0, bn, kb, c.z_in, pol_b);
+                            else ptx::tma_load_3d(sb, &tmB, bar, k0, bn, c.z_in, pol_b);
                         } else {
 #pragma unroll
                             for (int j = 0; j < SUB_ROWS / 64; ++j)
-                                ptx::tma_load_3d(sb + j * half, &tmB, bar, bn + j * 64, k0, c.z_in);
+                                ptx::tma_load_3d(sb + j * half, &tmB, bar, bn + j * 64, k0, c.z_in, pol_b);
                         }
                         ++issued;
                         if (++stage == stages) {
@@ -480,12 +511,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                         ptx::mbar_expect_tx(bar, step_bytes);
                     }
                     if (p.a_mn_major == 0u) {
-                        tma_load<CL>(sa, &tmA, bar, k0, am, c.z_in);
+                        tma_load<CL>(sa, &tmA, bar, k0, am, c.z_in, pol_a);
                     } else {
 #pragma unroll
                         for (int j = 0; j < BLOCK_M / 64; ++j)
                             tma_load<CL>(sa + j * (64 * BLOCK_K * 2), &tmA, bar, am + j * 64, k0,
-                                         c.z_in);
+                                         c.z_in, pol_a);
                     }
 #pragma unroll
                     for (int h = 0; h < NSUB; ++h) {
@@ -493,13 +524,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                         const int32_t  bh = bn + h * UMMA_N; // first B' row of sub-tile h
                         const uint32_t sh = sb + h * SUB_BYTES;
                         if (p.b_mn_major == 0u) {
-                            tma_load<CL>(sh, &tmB, bar, k0, bh, c.z_in);
+                            tma_load<CL>(sh, &tmB, bar, k0, bh, c.z_in, pol_b);
                         } else {
 #pragma unroll
                             for (int j = 0; j < SUB_ROWS / 64; ++j)
                                 if (!FLEX || static_cast<uint32_t>(j) * 64u < sub_rows)
                                     tma_load<CL>(sh + j * (64 * BLOCK_K * 2), &tmB, bar, bh + j * 64,
-                                                 k0, c.z_in);
+                                                 k0, c.z_in, pol_b);
                         }
                     }
                     ++issued;
@@ -677,6 +708,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         const uint32_t stg  = epi + q * 2u * EPI_BUF_BYTES;
         uint32_t       it   = 0, nstore = 0;
         bool           ok   = true;
+        const uint64_t pol_d = ptx::make_l2_policy((p.l2_hints >> 4) & 3u);
         for (uint32_t w = unit; ok && w < p.num_work; w += units, ++it) {
             const WorkCoord c      = decode_work(p, w, wn, tile_m);
             const uint32_t  buf    = it % NUM_ACC;
@@ -786,7 +818,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                     ptx::fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        ptx::tma_store_3d(&tmD, sbuf, col0, row0, c.z_out);
+                        if constexpr (GATHER) {
+                            // The tile goes to every copy of the full matrix (this GPU's and its
+                            // peers', over NVLink) at the slab's offset: the all-gather of the
+                            // output happens tile by tile under the main loop of the next tile.
+                            for (uint32_t d = 0; d < p.ndst; ++d)
+                                ptx::tma_store_3d(&tmDs[d], sbuf, col0 + p.dst_col0, row0 + p.dst_row0, c.z_out, pol_d);
+                        } else {
+                            ptx::tma_store_3d(&tmD, sbuf, col0, row0, c.z_out, pol_d);
+                        }
                         ptx::tma_store_commit();
                     }
                     ++nstore;
@@ -809,6 +849,28 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
         __syncwarp();
         ptx::tmem_dealloc<CL>(tmem_base, TMEM_COLS);
     }
+}
+
+template <int BN, int OUT, int CL, bool TR = false>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA,
+                     const __grid_constant__ CUtensorMap tmB,
+                     const __grid_constant__ CUtensorMap tmD, const GemmParams p)
+{
+    gemm_umma_body<BN, OUT, CL, TR, false>(tmA, tmB, &tmD, p);
+}
+
+// The same GEMM with the all-gather of its output fused into the epilogue: this GPU computes a
+// slab of a larger matrix and stores every tile of it into p.ndst copies of that matrix (its own
+// and, through peer mappings, the other GPUs').  Plain TMA stores to peer memory: no loads from
+// a peer, no multicast, and no wait on another GPU anywhere in the kernel.
+template <int BN, int OUT, int CL>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    gemm_umma_gather_kernel(const __grid_constant__ CUtensorMap tmA,
+                            const __grid_constant__ CUtensorMap tmB,
+                            const __grid_constant__ GatherMaps dst, const GemmParams p)
+{
+    gemm_umma_body<BN, OUT, CL, false, true>(tmA, tmB, dst.m, p);
 }
 
 // ---------------------------------------------------------------------------------------------

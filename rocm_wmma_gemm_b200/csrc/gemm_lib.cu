@@ -151,19 +151,35 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// Co-resident CTA pairs of the three pair kernels (tile_n 128 / 256 / 512), as the occupancy
+// query answered for the dynamic shared memory size it was asked with (0 = not asked yet).
+struct PairCache {
+    int      units[3] = {0, 0, 0};
+    uint32_t smem[3]  = {0, 0, 0};
+};
+
 struct DeviceCtx {
     std::atomic<bool> ready{false}; // set last, read first: initialised contexts skip the lock
     int           sm_count = 0;
-    int           pair_units[3] = {0, 0, 0}; // co-resident CTA pairs for tile_n 128 / 256 / 512 (0 = not asked yet)
+    PairCache     pairs;
     unsigned int* d_status = nullptr;
     // split-K workspaces, one per stream that has used split-K (calls on one stream are ordered,
-    // so they can share a buffer; calls on different streams must not)
+    // so they can share a buffer; calls on different streams must not - and two host threads
+    // must not issue calls on the same stream at the same time)
     struct Workspace {
         cudaStream_t stream;
         float*       ptr;
         size_t       bytes;
     };
     std::vector<Workspace> workspaces;
+    // buffers a workspace has outgrown: freed once the work that was queued on them has drained
+    struct Retired {
+        float*      ptr;
+        cudaEvent_t drained;
+    };
+    std::vector<Retired> retired;
+    std::mutex           ws_mutex;   // guards workspaces / retired
+    std::mutex           host_mutex; // held for the whole of a host-buffer call
     // host-buffer path: compute stream, copy-in / copy-out streams and the events chaining them
     cudaStream_t h_in = nullptr, h_out = nullptr;
     cudaEvent_t  h_ev_a[16] = {}, h_ev_b[16] = {}, h_ev_done[256] = {};
@@ -186,6 +202,11 @@ static cudaError_t set_smem_attr_one()
     if (e == cudaSuccess && CL == 2)
         e = cudaFuncSetAttribute(gemm_umma_kernel<BN, OUT, CL>,
                                  cudaFuncAttributeNonPortableClusterSizeAllowed, 0);
+    if constexpr (CL == 2 && BN >= 256) {
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemm_umma_gather_kernel<BN, OUT, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)gemm_smem_bytes(BN, CL, max_stages(BN, CL)));
+    }
     return e;
 }
 
@@ -216,6 +237,22 @@ static cudaError_t set_smem_attr_narrow()
     cudaError_t e = set_smem_attr_narrow_one<BN, OUT_F32>();
     if (e == cudaSuccess) e = set_smem_attr_narrow_one<BN, OUT_F16>();
     if (e == cudaSuccess) e = set_smem_attr_narrow_one<BN, OUT_BF16>();
+    return e;
+}
+
+// Opt every compiled GEMM kernel in to the dynamic shared memory it may be launched with.
+static cudaError_t set_all_kernel_attributes()
+{
+    cudaError_t e = set_smem_attr<64, 1>();
+    if (e == cudaSuccess) e = set_smem_attr<128, 1>();
+    if (e == cudaSuccess) e = set_smem_attr<256, 1>();
+    if (e == cudaSuccess) e = set_smem_attr<128, 2>();
+    if (e == cudaSuccess) e = set_smem_attr<256, 2>();
+    if (e == cudaSuccess) e = set_smem_attr<512, 2>();
+    if (e == cudaSuccess) e = set_smem_attr_narrow<16>();
+    if (e == cudaSuccess) e = set_smem_attr_narrow<32>();
+    if (e == cudaSuccess) e = set_smem_attr_narrow<64>();
+    if (e == cudaSuccess) e = set_smem_attr_narrow<128>();
     return e;
 }
 
@@ -251,16 +288,7 @@ static int get_ctx(DeviceCtx** out)
         }
         CUDA_TRY(cudaMalloc(&c.d_status, sizeof(unsigned int)));
         CUDA_TRY(cudaMemset(c.d_status, 0, sizeof(unsigned int)));
-        CUDA_TRY((set_smem_attr<64, 1>()));
-        CUDA_TRY((set_smem_attr<128, 1>()));
-        CUDA_TRY((set_smem_attr<256, 1>()));
-        CUDA_TRY((set_smem_attr<128, 2>()));
-        CUDA_TRY((set_smem_attr<256, 2>()));
-        CUDA_TRY((set_smem_attr<512, 2>()));
-        CUDA_TRY((set_smem_attr_narrow<16>()));
-        CUDA_TRY((set_smem_attr_narrow<32>()));
-        CUDA_TRY((set_smem_attr_narrow<64>()));
-        CUDA_TRY((set_smem_attr_narrow<128>()));
+        CUDA_TRY(set_all_kernel_attributes());
         c.ready.store(true, std::memory_order_release);
     }
     *out = &c;
@@ -269,19 +297,39 @@ static int get_ctx(DeviceCtx** out)
 
 // Split-K workspace of at least `bytes` for `stream`: cached per stream and grown on demand, so
 // the steady state allocates nothing (an allocation per call costs more than a skinny GEMM).
+// A buffer that has become too small is not freed here - kernels queued on the stream may still
+// use it - but retired behind an event and freed by a later call once that event has passed.
 static int get_workspace(DeviceCtx* ctx, cudaStream_t stream, size_t bytes, float** out)
 {
-    std::lock_guard<std::mutex> lock(g_mutex);
+    std::lock_guard<std::mutex> lock(ctx->ws_mutex);
+    for (size_t i = 0; i < ctx->retired.size();) {
+        if (cudaEventQuery(ctx->retired[i].drained) == cudaSuccess) {
+            cudaFree(ctx->retired[i].ptr);
+            cudaEventDestroy(ctx->retired[i].drained);
+            ctx->retired[i] = ctx->retired.back();
+            ctx->retired.pop_back();
+        } else {
+            (void)cudaGetLastError(); // cudaErrorNotReady is not an error of ours
+            ++i;
+        }
+    }
     for (auto& w : ctx->workspaces) {
         if (w.stream != stream) continue;
         if (w.bytes < bytes) {
-            // The old buffer may still be in use by work queued on this stream.
-            CUDA_TRY(cudaStreamSynchronize(stream));
-            CUDA_TRY(cudaFree(w.ptr));
-            w.ptr   = nullptr;
-            w.bytes = 0;
-            const size_t want = bytes + bytes / 4;
-            CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&w.ptr), want));
+            const size_t want  = bytes + bytes / 4;
+            float*       fresh = nullptr;
+            CUDA_TRY(cudaMalloc(reinterpret_cast<void**>(&fresh), want));
+            DeviceCtx::Retired r{w.ptr, nullptr};
+            if (cudaEventCreateWithFlags(&r.drained, cudaEventDisableTiming) == cudaSuccess &&
+                cudaEventRecord(r.drained, stream) == cudaSuccess) {
+                ctx->retired.push_back(r);
+            } else { // no event to wait behind: drain the stream, then free
+                (void)cudaGetLastError();
+                if (r.drained) cudaEventDestroy(r.drained);
+                cudaStreamSynchronize(stream);
+                cudaFree(w.ptr);
+            }
+            w.ptr   = fresh;
             w.bytes = want;
         }
         *out = w.ptr;
@@ -418,7 +466,9 @@ static int check_config(const b200_gemm_config& c)
     if (c.cluster == 1 && c.tile_n == 512) return fail(B200_GEMM_ERR_BAD_CONFIG, "tile_n 512 needs cluster 2");
     if (c.stages < 2 || c.stages > MAX_STAGES) return fail(B200_GEMM_ERR_BAD_CONFIG, "stages %d outside 2..%d", c.stages, MAX_STAGES);
     if (c.split_k < 1 || c.split_k > 64) return fail(B200_GEMM_ERR_BAD_CONFIG, "split_k %d outside 1..64", c.split_k);
-    if (c.raster < 0 || c.raster > 64) return fail(B200_GEMM_ERR_BAD_CONFIG, "raster %d outside 0..64", c.raster);
+    if (c.raster < 0 || (c.raster & ~B200_GEMM_RASTER_SNAKE) > 64)
+        return fail(B200_GEMM_ERR_BAD_CONFIG, "raster %d: band height outside 0..64 (add %d for the snake order)", c.raster,
+                    B200_GEMM_RASTER_SNAKE);
     return B200_GEMM_OK;
 }
 
@@ -587,15 +637,16 @@ static int encode_operand_slab(CUtensorMap* tm, bool bf16, const void* base, uin
 // Launch
 // ------------------------------------------------------------------------------------------
 template <int BN, int CL, bool TR = false>
-static cudaError_t launch_bn(int out, uint32_t units_wanted, int* pair_units, uint32_t smem, cudaStream_t s,
+static cudaError_t launch_bn(int out, uint32_t units_wanted, PairCache* pairs, int pair_slot, uint32_t smem, cudaStream_t s,
                              const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& d,
-                             const GemmParams& gp)
+                             const GemmParams& gp, const GatherMaps* gather = nullptr)
 {
     cudaLaunchConfig_t lc = {};
     dim3               grid(CL * units_wanted);
     if (CL == 2) {
         // A persistent pair kernel wants exactly as many clusters as can be resident at once.
-        if (*pair_units == 0) {
+        int&      pair_units = pairs->units[pair_slot];
+        if (pair_units == 0 || pairs->smem[pair_slot] != smem) {
             cudaLaunchConfig_t q = {};
             q.gridDim            = dim3(2 * 148);
             q.blockDim           = dim3(GEMM_THREADS);
@@ -613,9 +664,10 @@ static cudaError_t launch_bn(int out, uint32_t units_wanted, int* pair_units, ui
                 (void)cudaGetLastError();
                 n = 64;
             }
-            *pair_units = n;
+            pair_units             = n;
+            pairs->smem[pair_slot] = smem;
         }
-        grid = dim3(2 * std::min<uint32_t>(units_wanted, (uint32_t)*pair_units));
+        grid = dim3(2 * std::min<uint32_t>(units_wanted, (uint32_t)pair_units));
     }
     lc.gridDim            = grid;
     lc.blockDim           = dim3(GEMM_THREADS);
@@ -631,6 +683,15 @@ static cudaError_t launch_bn(int out, uint32_t units_wanted, int* pair_units, ui
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs                                           = attr;
     lc.numAttrs                                        = 2;
+    if constexpr (CL == 2 && BN >= 256 && !TR) {
+        if (gather) { // the gathering twins exist for the two large pair tiles
+            switch (out) {
+                case OUT_F32: return cudaLaunchKernelEx(&lc, gemm_umma_gather_kernel<BN, OUT_F32, CL>, a, b, *gather, gp);
+                case OUT_F16: return cudaLaunchKernelEx(&lc, gemm_umma_gather_kernel<BN, OUT_F16, CL>, a, b, *gather, gp);
+                default: return cudaLaunchKernelEx(&lc, gemm_umma_gather_kernel<BN, OUT_BF16, CL>, a, b, *gather, gp);
+            }
+        }
+    }
     switch (out) {
         case OUT_F32: return cudaLaunchKernelEx(&lc, gemm_umma_kernel<BN, OUT_F32, CL, TR>, a, b, d, gp);
         case OUT_F16: return cudaLaunchKernelEx(&lc, gemm_umma_kernel<BN, OUT_F16, CL, TR>, a, b, d, gp);
@@ -806,6 +867,48 @@ static int make_plan(const Problem& p, const b200_gemm_config* user_cfg, int sm_
     return B200_GEMM_OK;
 }
 
+// Where a launch gets its device-side resources from.  The ordinary entry points use the
+// per-device context (status word and split-K workspaces from cudaMalloc); the allocation-free
+// entry point uses arrays that are part of the library image and must never allocate.
+struct LaunchEnv {
+    int           sm_count;
+    unsigned int* d_status;     // device status word the kernels report give-ups to
+    PairCache*    pairs;
+    DeviceCtx*    ctx;          // owner of the cached split-K workspaces; nullptr = fixed workspace
+    float*        fixed_ws;     // ctx == nullptr: the built-in workspace (device address) ...
+    size_t        fixed_ws_bytes; // ... and its size
+};
+
+// L2 eviction priorities of the TMA traffic (GemmParams::l2_hints).  B200_GEMM_L2_HINTS, read
+// once, overrides the launch path's own choice (profiling).
+static int env_l2_hints()
+{
+    static const int v = [] {
+        const char* e = getenv("B200_GEMM_L2_HINTS");
+        return (e && *e) ? atoi(e) : -1;
+    }();
+    return v;
+}
+
+// The launch path's own choice of L2 eviction priorities for the TMA traffic of one problem.
+static uint32_t default_l2_hints(const View& v, const GemmParams& gp, size_t batch, size_t out_sz)
+{
+    (void)v; (void)gp; (void)batch; (void)out_sz;
+    return 0u;
+}
+
+// A GEMM whose output is a block of a larger matrix held once per GPU: every tile is stored to
+// all `ndst` copies (fused all-gather).  In the caller's terms the problem's C (M x N, layout
+// lc) is the block at (row0, col0) of a full_rows x full_cols matrix of the same layout.
+struct GatherSpec {
+    void* const* dst;   // ndst base addresses (this GPU's copy and peer mappings of the others')
+    int          ndst;
+    size_t       full_rows, full_cols, row0, col0;
+};
+
+static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_config* user_cfg, const LaunchEnv& env,
+                       const GatherSpec* gather = nullptr);
+
 static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_config* user_cfg)
 {
     int st = validate(p);
@@ -821,10 +924,29 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
         CUDA_TRY(cudaMemsetAsync(p.C, 0, p.M * p.N * p.batch * out_sz, stream));
         return B200_GEMM_OK;
     }
+    const LaunchEnv env{ctx->sm_count, ctx->d_status, &ctx->pairs, ctx, nullptr, 0};
+    return launch_gemm(p, stream, user_cfg, env);
+}
 
+// Plans and launches one (validated, non-empty) problem.
+static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_config* user_cfg, const LaunchEnv& env,
+                       const GatherSpec* gather)
+{
+    int        st;
+    const bool fixed = env.ctx == nullptr;
     LaunchPlan pl;
-    st = make_plan(p, user_cfg, ctx->sm_count, &pl);
+    st = make_plan(p, user_cfg, env.sm_count, &pl);
     if (st != B200_GEMM_OK) return st;
+    if (pl.generic && fixed)
+        return fail(B200_GEMM_ERR_MISALIGNED,
+                    "the allocation-free entry point needs 16-byte aligned pointers and contiguous extents that are "
+                    "multiples of 8 elements (M=%zu N=%zu K=%zu)", p.M, p.N, p.K);
+    if (gather && (pl.generic || pl.transposed || pl.cfg.split_k != 1 || pl.cfg.cluster != 2 || pl.cfg.tile_n < 256 ||
+                   p.batch != 1))
+        return fail(B200_GEMM_ERR_BAD_CONFIG,
+                    "the fused gather needs a plan on the 256-row pair tiles without K partitions (got %s, tile_n %d, cluster %d, "
+                    "split_k %d, batch %zu)", pl.generic ? "the CUDA-core kernel" : (pl.transposed ? "the operand swap" : "a tcgen05 tile"),
+                    pl.cfg.tile_n, pl.cfg.cluster, pl.cfg.split_k, p.batch);
     if (pl.generic) {
         cudaError_t e;
         switch (p.types) {
@@ -866,7 +988,8 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     gp.k_blocks     = (v.K + BLOCK_K - 1) / BLOCK_K;
     gp.split_k      = split;
     gp.kb_per_split = kb_per_split;
-    gp.group_m      = (uint32_t)cfg.raster;
+    gp.group_m      = (uint32_t)(cfg.raster & ~B200_GEMM_RASTER_SNAKE);
+    gp.snake        = (cfg.raster & B200_GEMM_RASTER_SNAKE) ? 1u : 0u;
     const uint64_t work = (uint64_t)gp.batch * split * gp.m_tiles * gp.n_tiles;
     if (work > 0x7fffffffull) return fail(B200_GEMM_ERR_BAD_SIZE, "too many tiles (%llu)", (unsigned long long)work);
     gp.num_work   = (uint32_t)work;
@@ -879,8 +1002,11 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     gp.idesc = (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | (gp.a_mn_major << 15) |
                (gp.b_mn_major << 16) | ((uint32_t)(umma_n >> 3) << 17) | ((uint32_t)((BLOCK_M * cl) >> 4) << 24);
     gp.stages = (uint32_t)cfg.stages;
-    gp.status = ctx->d_status;
+    gp.status = env.d_status;
     gp.out    = nullptr;
+    gp.ndst = 0;
+    gp.dst_row0 = gp.dst_col0 = 0;
+    gp.l2_hints = env_l2_hints() >= 0 ? (uint32_t)env_l2_hints() : default_l2_hints(v, gp, p.batch, out_is_f32(p.types) ? 4 : 2);
     // 512-wide tiles stagger their two column halves so the epilogue of one half hides under the
     // MMAs of the other (TileStep in gemm_kernels.cuh).  The stagger covers the time one half
     // takes to drain: about 5.5k cycles for f32 output, 3.3k for 16-bit, at 512 cycles per k-block.
@@ -892,7 +1018,7 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     // Streaming (HBM-bound) views rotate the K order per work unit; see the producer.
     const bool streaming = narrow || std::min(v.M, v.N) <= 256;
     const uint32_t slots_per_unit = (kb_per_split + kc - 1) / kc; // K steps of one work unit
-    gp.k_skew = streaming ? std::max<uint32_t>(1u, slots_per_unit / std::max<uint32_t>(1u, std::min<uint32_t>((uint32_t)work, (uint32_t)ctx->sm_count))) : 0u;
+    gp.k_skew = streaming ? std::max<uint32_t>(1u, slots_per_unit / std::max<uint32_t>(1u, std::min<uint32_t>((uint32_t)work, (uint32_t)env.sm_count))) : 0u;
 
     // Split-K partials go to this stream's cached f32 workspace, laid out [batch][split][Mk][Nk].
     float*       ws       = nullptr;
@@ -900,16 +1026,25 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     bool         ws_stream_ordered = false;
     if (split > 1) {
         if (!transposed && v.N % 4) return fail(B200_GEMM_ERR_BAD_CONFIG, "split_k needs N %% 4 == 0 in the kernel view");
-        // While the stream is being captured into a graph nothing may be allocated with
-        // cudaMalloc; a stream-ordered allocation becomes part of the graph instead.
-        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-        CUDA_TRY(cudaStreamIsCapturing(stream, &cap));
-        if (cap != cudaStreamCaptureStatusNone) {
-            CUDA_TRY(cudaMallocAsync(reinterpret_cast<void**>(&ws), ws_bytes, stream));
-            ws_stream_ordered = true;
+        if (fixed) {
+            if (ws_bytes > env.fixed_ws_bytes)
+                return fail(B200_GEMM_ERR_TOO_LARGE,
+                            "split-K partials need %zu bytes (batch %zu x split %u x %u x %u x 4) but the built-in workspace "
+                            "holds %zu; use fewer partitions or the allocating entry points",
+                            ws_bytes, p.batch, split, v.M, v.N, env.fixed_ws_bytes);
+            ws = env.fixed_ws;
         } else {
-            st = get_workspace(ctx, stream, ws_bytes, &ws);
-            if (st != B200_GEMM_OK) return st;
+            // While the stream is being captured into a graph nothing may be allocated with
+            // cudaMalloc; a stream-ordered allocation becomes part of the graph instead.
+            cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+            CUDA_TRY(cudaStreamIsCapturing(stream, &cap));
+            if (cap != cudaStreamCaptureStatusNone) {
+                CUDA_TRY(cudaMallocAsync(reinterpret_cast<void**>(&ws), ws_bytes, stream));
+                ws_stream_ordered = true;
+            } else {
+                st = get_workspace(env.ctx, stream, ws_bytes, &ws);
+                if (st != B200_GEMM_OK) return st;
+            }
         }
     }
 
@@ -933,6 +1068,25 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
             st = encode_map(&tmD, out == OUT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                             v.d, v.N, v.M, p.batch, 64, 32);
     }
+    GatherMaps gmaps;
+    if (st == B200_GEMM_OK && gather) {
+        // Kernel view of the full matrix: a column-major C is the row-major transpose, so rows
+        // and columns (and the block's offsets) swap with it.
+        const bool     sw    = p.lc != 0;
+        const uint64_t frows = sw ? gather->full_cols : gather->full_rows;
+        const uint64_t fcols = sw ? gather->full_rows : gather->full_cols;
+        gp.dst_row0          = (uint32_t)(sw ? gather->col0 : gather->row0);
+        gp.dst_col0          = (uint32_t)(sw ? gather->row0 : gather->col0);
+        gp.ndst              = (uint32_t)gather->ndst;
+        for (int d = 0; st == B200_GEMM_OK && d < gather->ndst; ++d) {
+            if (out == OUT_F32)
+                st = encode_map(&gmaps.m[d], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, gather->dst[d], fcols, frows, 1, 32, 32);
+            else
+                st = encode_map(&gmaps.m[d], out == OUT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                                2, gather->dst[d], fcols, frows, 1, 64, 32);
+        }
+        for (int d = gather->ndst; d < MAX_GATHER_DST; ++d) gmaps.m[d] = gmaps.m[0];
+    }
     if (st != B200_GEMM_OK) {
         if (ws_stream_ordered) cudaFreeAsync(ws, stream);
         return st;
@@ -940,27 +1094,27 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
 
     const uint32_t smem     = transposed ? slab_smem_bytes((int)bm, bn, (int)kc, cfg.stages)
                               : (slot ? slot_smem_bytes(bn, (int)kc, cfg.stages) : gemm_smem_bytes(compiled_width(bn), (int)cl, cfg.stages));
-    const uint32_t units    = std::min<uint32_t>(gp.num_work, (uint32_t)ctx->sm_count / cl);
+    const uint32_t units    = std::min<uint32_t>(gp.num_work, (uint32_t)env.sm_count / cl);
     const int      kern_out = split > 1 ? OUT_F32 : out;
     cudaError_t    e;
     if (transposed) {
         switch (bn) {
-            case 16: e = launch_bn<16, 1, true>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
-            case 32: e = launch_bn<32, 1, true>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
-            case 64: e = launch_bn<64, 1, true>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
-            default: e = launch_bn<128, 1, true>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
+            case 16: e = launch_bn<16, 1, true>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, gp); break;
+            case 32: e = launch_bn<32, 1, true>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, gp); break;
+            case 64: e = launch_bn<64, 1, true>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, gp); break;
+            default: e = launch_bn<128, 1, true>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, gp); break;
         }
     } else if (cl == 2) {
-        if (bn <= 128) e = launch_bn<128, 2>(kern_out, units, &ctx->pair_units[0], smem, stream, tmA, tmB, tmD, gp);
-        else if (bn <= 256) e = launch_bn<256, 2>(kern_out, units, &ctx->pair_units[1], smem, stream, tmA, tmB, tmD, gp);
-        else e = launch_bn<512, 2>(kern_out, units, &ctx->pair_units[2], smem, stream, tmA, tmB, tmD, gp);
+        if (bn <= 128) e = launch_bn<128, 2>(kern_out, units, env.pairs, 0, smem, stream, tmA, tmB, tmD, gp);
+        else if (bn <= 256) e = launch_bn<256, 2>(kern_out, units, env.pairs, 1, smem, stream, tmA, tmB, tmD, gp, gather ? &gmaps : nullptr);
+        else e = launch_bn<512, 2>(kern_out, units, env.pairs, 2, smem, stream, tmA, tmB, tmD, gp, gather ? &gmaps : nullptr);
     } else {
         switch (bn) {
-            case 16: e = launch_bn<16, 1>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
-            case 32: e = launch_bn<32, 1>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
-            case 64: e = launch_bn<64, 1>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
-            case 128: e = launch_bn<128, 1>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
-            default: e = launch_bn<256, 1>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
+            case 16: e = launch_bn<16, 1>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, gp); break;
+            case 32: e = launch_bn<32, 1>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, gp); break;
+            case 64: e = launch_bn<64, 1>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, gp); break;
+            case 128: e = launch_bn<128, 1>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, gp); break;
+            default: e = launch_bn<256, 1>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, gp); break;
         }
     }
     g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -973,7 +1127,7 @@ static int run_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_confi
     if (split > 1) {
         const uint64_t mn     = (uint64_t)v.M * v.N;
         const uint64_t total4 = mn * p.batch / 4;
-        const unsigned blocks = (unsigned)std::min<uint64_t>((total4 + 255) / 256, (uint64_t)ctx->sm_count * 8);
+        const unsigned blocks = (unsigned)std::min<uint64_t>((total4 + 255) / 256, (uint64_t)env.sm_count * 8);
         e = launch_reduce(out, blocks, stream, ws, v.d, mn, split, (uint32_t)p.batch);
         g_launches.fetch_add(1, std::memory_order_relaxed);
         if (ws_stream_ordered) cudaFreeAsync(ws, stream);
@@ -1012,14 +1166,14 @@ static int run_from_abi(int types, void* C, const void* A, const void* B, size_t
 // device addresses come from cudaGetSymbolAddress, asked once per device with that device
 // current, and only those are handed to kernels and TMA descriptors.
 static __device__ __align__(256) float        g_static_workspace[B200_GEMM_STATIC_WORKSPACE_BYTES / sizeof(float)];
-static __device__ __align__(256) unsigned int g_static_status[64];
+static __device__ __align__(256) unsigned int g_static_status[1];
 
 struct StaticCtx {
     bool          ready    = false;
     int           sm_count = 0;
     float*        d_ws     = nullptr; // device address of g_static_workspace on this device
     unsigned int* d_status = nullptr; // device address of g_static_status on this device
-    int           pair_units[3] = {0, 0, 0};
+    PairCache     pairs;
 };
 static StaticCtx g_static_ctx[k_max_devices];
 
@@ -1050,18 +1204,15 @@ static int get_static_ctx(StaticCtx** out)
         }
         CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&c.d_ws), g_static_workspace));
         CUDA_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&c.d_status), g_static_status));
-        CUDA_TRY((set_smem_attr<64, 1>()));
-        CUDA_TRY((set_smem_attr<128, 1>()));
-        CUDA_TRY((set_smem_attr<256, 1>()));
-        CUDA_TRY((set_smem_attr<128, 2>()));
-        CUDA_TRY((set_smem_attr<256, 2>()));
-        CUDA_TRY((set_smem_attr<512, 2>()));
+        CUDA_TRY(set_all_kernel_attributes());
         c.ready = true;
     }
     *out = &c;
     return B200_GEMM_OK;
 }
 
+// The allocation-free twin of run_gemm: same planning and launch code (launch_gemm), with the
+// status word and the split-K workspace taken from the arrays above.
 static int run_gemm_static(const Problem& p, cudaStream_t stream, const b200_gemm_config* user_cfg)
 {
     int st = validate(p);
@@ -1072,110 +1223,8 @@ static int run_gemm_static(const Problem& p, cudaStream_t stream, const b200_gem
     StaticCtx* ctx = nullptr;
     st             = get_static_ctx(&ctx);
     if (st != B200_GEMM_OK) return st;
-
-    const View v = make_view(p);
-    if (!tma_ok(p, v))
-        return fail(B200_GEMM_ERR_MISALIGNED,
-                    "the allocation-free entry point needs 16-byte aligned pointers and contiguous extents that are "
-                    "multiples of 8 elements (M=%zu N=%zu K=%zu)", p.M, p.N, p.K);
-
-    b200_gemm_config cfg = resolve_config(p, user_cfg, nullptr);
-    st                   = check_config(cfg);
-    if (st != B200_GEMM_OK) return st;
-    cfg.tile_n = compiled_width(cfg.tile_n); // this entry point keeps to the compiled tile widths
-    uint32_t kb_per_split = 0;
-    legalize(cfg, v, &kb_per_split);
-
-    const int      bn    = cfg.tile_n;
-    const int      out   = out_kind(p.types);
-    const bool     bf16  = in_is_bf16(p.types);
-    const uint32_t split = (uint32_t)cfg.split_k;
-    const uint32_t cl    = (uint32_t)cfg.cluster;
-
-    const size_t ws_bytes = split > 1 ? (size_t)p.batch * split * v.M * v.N * sizeof(float) : 0;
-    if (ws_bytes > (size_t)B200_GEMM_STATIC_WORKSPACE_BYTES)
-        return fail(B200_GEMM_ERR_TOO_LARGE,
-                    "split-K partials need %zu bytes (batch %zu x split %u x %u x %u x 4) but the built-in workspace "
-                    "holds %zu; use fewer partitions or the allocating entry points",
-                    ws_bytes, p.batch, split, v.M, v.N, (size_t)B200_GEMM_STATIC_WORKSPACE_BYTES);
-    if (split > 1 && v.N % 4) return fail(B200_GEMM_ERR_BAD_CONFIG, "split_k needs N %% 4 == 0 in the kernel view");
-
-    GemmParams gp;
-    gp.M            = v.M;
-    gp.N            = v.N;
-    gp.K            = v.K;
-    gp.batch        = (uint32_t)p.batch;
-    gp.bm           = BLOCK_M;
-    gp.wn           = (uint32_t)cfg.tile_n;
-    gp.kc           = 1;
-    gp.k4d          = 0;
-    gp.m_tiles      = (v.M + BLOCK_M * cl - 1) / (BLOCK_M * cl);
-    gp.n_tiles      = (v.N + bn - 1) / bn;
-    gp.k_blocks     = (v.K + BLOCK_K - 1) / BLOCK_K;
-    gp.split_k      = split;
-    gp.kb_per_split = kb_per_split;
-    gp.group_m      = (uint32_t)cfg.raster;
-    const uint64_t work = (uint64_t)gp.batch * split * gp.m_tiles * gp.n_tiles;
-    if (work > 0x7fffffffull) return fail(B200_GEMM_ERR_BAD_SIZE, "too many tiles (%llu)", (unsigned long long)work);
-    gp.num_work      = (uint32_t)work;
-    const int umma_n = bn > 256 ? 256 : bn;
-    gp.a_mn_major    = v.a_mn ? 1u : 0u;
-    gp.b_mn_major    = v.b_mn ? 1u : 0u;
-    gp.idesc = (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | (gp.a_mn_major << 15) |
-               (gp.b_mn_major << 16) | ((uint32_t)(umma_n >> 3) << 17) | ((uint32_t)((BLOCK_M * cl) >> 4) << 24);
-    gp.stages = (uint32_t)cfg.stages;
-    gp.status = ctx->d_status;
-    gp.out    = nullptr;
-    gp.k_skew = 0;
-    gp.stagger = 0;
-
-    float*      ws = ctx->d_ws; // device address resolved by cudaGetSymbolAddress, never the symbol itself
-    CUtensorMap tmA, tmB, tmD;
-    st = encode_operand(&tmA, bf16, v.a, v.M, v.K, p.batch, v.a_mn, BLOCK_M);
-    if (st == B200_GEMM_OK) st = encode_operand(&tmB, bf16, v.b, v.N, v.K, p.batch, v.b_mn, (uint32_t)umma_n / cl);
-    if (st == B200_GEMM_OK) {
-        if (split > 1)
-            st = encode_map(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ws, v.N, v.M, (uint64_t)p.batch * split, 32, 32);
-        else if (out == OUT_F32)
-            st = encode_map(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, v.d, v.N, v.M, p.batch, 32, 32);
-        else
-            st = encode_map(&tmD, out == OUT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                            v.d, v.N, v.M, p.batch, 64, 32);
-    }
-    if (st != B200_GEMM_OK) return st;
-
-    const uint32_t smem     = gemm_smem_bytes(bn, (int)cl, cfg.stages);
-    const uint32_t units    = std::min<uint32_t>(gp.num_work, (uint32_t)ctx->sm_count / cl);
-    const int      kern_out = split > 1 ? OUT_F32 : out;
-    cudaError_t    e;
-    if (cl == 2) {
-        if (bn == 128) e = launch_bn<128, 2>(kern_out, units, &ctx->pair_units[0], smem, stream, tmA, tmB, tmD, gp);
-        else if (bn == 256) e = launch_bn<256, 2>(kern_out, units, &ctx->pair_units[1], smem, stream, tmA, tmB, tmD, gp);
-        else e = launch_bn<512, 2>(kern_out, units, &ctx->pair_units[2], smem, stream, tmA, tmB, tmD, gp);
-    } else {
-        switch (bn) {
-            case 64: e = launch_bn<64, 1>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
-            case 128: e = launch_bn<128, 1>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
-            default: e = launch_bn<256, 1>(kern_out, units, nullptr, smem, stream, tmA, tmB, tmD, gp); break;
-        }
-    }
-    g_launches.fetch_add(1, std::memory_order_relaxed);
-    if (e != cudaSuccess) return fail(B200_GEMM_ERR_CUDA, "GEMM kernel launch failed: %s", cudaGetErrorString(e));
-
-    if (split > 1) {
-        const uint64_t mn     = (uint64_t)v.M * v.N;
-        const uint64_t total4 = mn * p.batch / 4;
-        const unsigned blocks = (unsigned)std::min<uint64_t>((total4 + 255) / 256, (uint64_t)ctx->sm_count * 8);
-        switch (out) {
-            case OUT_F32: splitk_reduce_kernel<OUT_F32><<<blocks, 256, 0, stream>>>(ws, v.d, mn, split, (uint32_t)p.batch); break;
-            case OUT_F16: splitk_reduce_kernel<OUT_F16><<<blocks, 256, 0, stream>>>(ws, v.d, mn, split, (uint32_t)p.batch); break;
-            default: splitk_reduce_kernel<OUT_BF16><<<blocks, 256, 0, stream>>>(ws, v.d, mn, split, (uint32_t)p.batch); break;
-        }
-        g_launches.fetch_add(1, std::memory_order_relaxed);
-        e = cudaGetLastError();
-        if (e != cudaSuccess) return fail(B200_GEMM_ERR_CUDA, "split-K reduce launch failed: %s", cudaGetErrorString(e));
-    }
-    return B200_GEMM_OK;
+    const LaunchEnv env{ctx->sm_count, ctx->d_status, &ctx->pairs, nullptr, ctx->d_ws, (size_t)B200_GEMM_STATIC_WORKSPACE_BYTES};
+    return launch_gemm(p, stream, user_cfg, env);
 }
 
 } // namespace b200
@@ -1309,6 +1358,7 @@ extern "C" int b200_gemm_slab(size_t N, int world, int rank, size_t align, size_
 extern "C" int b200_gemm_host(int types, void* C, const void* A, const void* B, size_t M, size_t N, size_t K,
                               size_t batch_count, int layout_c, int layout_a, int layout_b)
 {
+    t_last_status = B200_GEMM_OK;
     const Problem p{types, C, A, B, M, N, K, batch_count, layout_c, layout_a, layout_b};
     int           st = validate(p);
     if (st != B200_GEMM_OK) return st;
@@ -1316,10 +1366,12 @@ extern "C" int b200_gemm_host(int types, void* C, const void* A, const void* B, 
     DeviceCtx* ctx = nullptr;
     st             = get_ctx(&ctx);
     if (st != B200_GEMM_OK) return st;
+    // One host-buffer call at a time per device: the staging buffers, the three streams and the
+    // events below are per device, and the call ends in a synchronise anyway.
+    std::lock_guard<std::mutex> host_lock(ctx->host_mutex);
     const size_t out_sz   = out_is_f32(types) ? 4 : 2;
     const size_t bytes[3] = {M * K * batch_count * 2, K * N * batch_count * 2, M * N * batch_count * out_sz};
     {
-        std::lock_guard<std::mutex> lock(g_mutex);
         if (!ctx->h_stream) CUDA_TRY(cudaStreamCreateWithFlags(&ctx->h_stream, cudaStreamNonBlocking));
         for (int i = 0; i < 3; ++i) {
             if (ctx->h_cap[i] < bytes[i]) {
@@ -1358,7 +1410,6 @@ extern "C" int b200_gemm_host(int types, void* C, const void* A, const void* B, 
     const size_t              nra = rb.size() - 1, ncb = cb.size() - 1;
     if (batch_count == 1 && nra * ncb >= 2 && bytes[0] + bytes[1] + bytes[2] >= (32u << 20) && K > 0) {
         {
-            std::lock_guard<std::mutex> lock(g_mutex);
             if (!ctx->h_in) {
                 CUDA_TRY(cudaStreamCreateWithFlags(&ctx->h_in, cudaStreamNonBlocking));
                 CUDA_TRY(cudaStreamCreateWithFlags(&ctx->h_out, cudaStreamNonBlocking));
@@ -1455,6 +1506,23 @@ extern "C" int b200_gemm_device_status(unsigned int* detail)
     return B200_GEMM_OK;
 }
 
+extern "C" int b200_gemm_static_status(unsigned int* detail)
+{
+    t_last_status  = B200_GEMM_OK;
+    StaticCtx* ctx = nullptr;
+    int        st  = get_static_ctx(&ctx);
+    if (st != B200_GEMM_OK) return st;
+    CUDA_TRY(cudaDeviceSynchronize());
+    unsigned int word = 0;
+    CUDA_TRY(cudaMemcpy(&word, ctx->d_status, sizeof(word), cudaMemcpyDeviceToHost));
+    if (detail) *detail = word;
+    if (word != 0) {
+        CUDA_TRY(cudaMemset(ctx->d_status, 0, sizeof(word)));
+        return fail(B200_GEMM_ERR_DEVICE_WAIT, "a kernel of the allocation-free entry point gave up on a bounded wait (status word 0x%x)", word);
+    }
+    return B200_GEMM_OK;
+}
+
 extern "C" int b200_gemm_last_status(void) { return t_last_status; }
 extern "C" const char* b200_gemm_last_error(void) { return t_last_error; }
 extern "C" const char* b200_gemm_version(void) { return "b200_gemm 0.1 (sm_100a)"; }
@@ -1475,3 +1543,5 @@ extern "C" int b200_gemm_splitk_static(int types, void* C, const void* A, const 
         return fail(B200_GEMM_ERR_CUDA, "unknown exception");
     }
 }
+
+#include "slab_driver.inc"

@@ -186,19 +186,40 @@ def test_linearity():
     assert torch.equal(outs[0] + outs[1], outs[2])
 
 
-BIG = [
-    # (types, M, N, K, la, lb, lc, distribution, sigma)
-    (3, 8192, 8192, 8192, 0, 1, 0, ("normal", 0.02), 4e-4),       # headline shape, bf16 -> f32
-    (3, 4096, 5120, 5120, 0, 1, 0, ("normal", 0.02), 4e-4),       # projection shape
-    (0, 4096, 4096, 4096, 1, 0, 1, ("uniform", 1.0), 1.0 / 3.0),  # fp16 -> fp16 square, A col / B row / C col
-    (1, 16, 8192, 8192, 0, 0, 0, ("uniform", 1.0), 1.0 / 3.0),    # skinny, B row-major
-    (1, 128, 28672, 8192, 0, 1, 0, ("uniform", 1.0), 1.0 / 3.0),  # skinny, B col-major
-    (2, 8192, 4096, 16384, 0, 1, 0, ("normal", 1.0), 1.0),        # slab of the 16384^3 bf16 -> bf16 problem
-]
+N02 = ("normal", 0.02)
+UNI = ("uniform", 1.0)
+BIG = (
+    # (types, M, N, K, la, lb, lc, distribution, sigma): every benchmarked shape under the config the tuned table
+    # gives it.  The headline shape (bf16 -> f32 8192^3) and the fp16 -> fp16 squares in all eight layouts:
+    [(3, 8192, 8192, 8192, la, lb, lc, N02, 4e-4) for (la, lb, lc) in LAYOUTS]
+    + [(0, n, n, n, la, lb, lc, UNI, 1.0 / 3.0) for n in (1024, 2048, 8192) for (la, lb, lc) in LAYOUTS]
+    + [
+        (0, 4096, 4096, 4096, 1, 0, 1, UNI, 1.0 / 3.0),   # fp16 -> fp16 square, A col / B row / C col
+        (0, 4096, 4096, 4096, 0, 1, 0, UNI, 1.0 / 3.0),
+        # projection shapes, bf16 -> f32, A row / B col / C row
+        (3, 4096, 4096, 2048, 0, 1, 0, N02, 4e-4),
+        (3, 4096, 5120, 5120, 0, 1, 0, N02, 4e-4),
+        (3, 8192, 28672, 8192, 0, 1, 0, N02, 4e-4),
+        (3, 8192, 8192, 28672, 0, 1, 0, N02, 4e-4),
+        # skinny fp16 -> f32, B row- and column-major
+        (1, 16, 8192, 8192, 0, 0, 0, UNI, 1.0 / 3.0),
+        (1, 16, 28672, 8192, 0, 1, 0, UNI, 1.0 / 3.0),
+        (1, 64, 8192, 8192, 0, 0, 0, UNI, 1.0 / 3.0),
+        (1, 64, 8192, 8192, 0, 1, 0, UNI, 1.0 / 3.0),
+        (1, 64, 28672, 8192, 0, 0, 0, UNI, 1.0 / 3.0),
+        (1, 64, 28672, 8192, 0, 1, 0, UNI, 1.0 / 3.0),
+        (1, 128, 8192, 8192, 0, 0, 0, UNI, 1.0 / 3.0),
+        (1, 128, 8192, 8192, 0, 1, 0, UNI, 1.0 / 3.0),
+        (1, 128, 28672, 8192, 0, 1, 0, UNI, 1.0 / 3.0),
+        # column slabs of the large bf16 -> bf16 problems (8 GPUs: 16384^3 and 32768 x 32768 x 8192)
+        (2, 16384, 2048, 16384, 0, 1, 0, ("normal", 1.0), 1.0),
+        (2, 8192, 4096, 16384, 0, 1, 0, ("normal", 1.0), 1.0),
+        (2, 32768, 4096, 8192, 0, 1, 0, ("normal", 1.0), 1.0),
+    ])
 
 
 @pytest.mark.parametrize("types,M,N,K,la,lb,lc,dist,sigma", BIG,
-                         ids=[f"{NAMES[b[0]]}-{b[1]}x{b[2]}x{b[3]}" for b in BIG])
+                         ids=[f"{NAMES[b[0]]}-{b[1]}x{b[2]}x{b[3]}-{'rc'[b[4]]}{'rc'[b[5]]}{'rc'[b[6]]}" for b in BIG])
 def test_full_size_sampled_rows_and_columns(types, M, N, K, la, lb, lc, dist, sigma):
     """Full-size shapes: whole rows and whole columns of C (first/last, tile boundaries, random)
     against the CPU oracle, which computes only the sampled elements."""
@@ -223,8 +244,8 @@ def test_full_size_sampled_rows_and_columns(types, M, N, K, la, lb, lc, dist, si
     assert not torch.isnan(Cl.float()).any()
 
     rng = np.random.default_rng(5)
-    rows = sorted(set([0, M - 1] + [r for r in (127, 128, 255, 256) if r < M] + list(rng.integers(0, M, 3))))
-    cols = sorted(set([0, N - 1] + [c for c in (255, 256, 511, 512) if c < N] + list(rng.integers(0, N, 3))))
+    rows = sorted(set([0, M - 1] + [r for r in (127, 128, 255, 256) if r < M] + list(rng.integers(0, M, 2))))
+    cols = sorted(set([0, N - 1] + [c for c in (255, 256, 511, 512) if c < N] + list(rng.integers(0, N, 2))))
     A_bits = Am.view(torch.int16).cpu().numpy().view(np.uint16).ravel()
     B_bits = Bm.view(torch.int16).cpu().numpy().view(np.uint16).ravel()
     eps = 0.0 if types in (1, 3) else (2.0 ** -8 if bf16 else 2.0 ** -11)
@@ -356,6 +377,46 @@ def test_concurrent_streams_and_threads():
     for i in range(4):
         for out in results[i]:
             check_parity(3, out, ref, K, SIGMA_UNIFORM, M, N, 0)
+
+
+def test_host_buffer_entry_point_from_two_threads():
+    """b200_gemm_host keeps its staging buffers, streams and events per device and serialises
+    callers: two host threads with different shapes (the second needs larger buffers, so the
+    cached ones are regrown between calls) both get their own result."""
+    import threading
+    shapes = [(2304, 2560, 512, 0, 0, 1), (3072, 4096, 768, 1, 1, 0)]
+    want, got, errors = {}, {}, []
+    inputs = {}
+    for i, (M, N, K, lc, la, lb) in enumerate(shapes):
+        A, B = seeded(M, N, K, la, lb, True)
+        inputs[i] = (A, B)
+        want[i] = gpu_gemm(3, A, B, M, N, K, lc, la, lb)
+
+    def work(i):
+        try:
+            M, N, K, lc, la, lb = shapes[i]
+            A, B = inputs[i]
+            ta, tb = torch.from_numpy(A.view(np.int16)).pin_memory(), torch.from_numpy(B.view(np.int16)).pin_memory()
+            outs = []
+            for _ in range(3):
+                tc = torch.full((M * N,), float("nan"), dtype=torch.float32).pin_memory()
+                g.loader().gemm_host(tc, ta, tb, M, N, K, lc, la, lb, types=3)
+                outs.append(tc.numpy().copy())
+            got[i] = outs
+        except Exception as ex:
+            errors.append(ex)
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for i in range(2):
+        for out in got[i]:
+            # the host path computes C in tiles, whose configurations may partition K differently
+            assert np.abs(out - want[i]).max() <= max(1e-4, f32_sum_tolerance(shapes[i][2], SIGMA_UNIFORM))
+    assert g.device_status() == 0
 
 
 SLAB_EDGES = [(16, 8200, 576), (33, 9000, 264), (64, 8192 + 56, 320), (8, 20000, 192), (16, 8192, 4096 + 64),

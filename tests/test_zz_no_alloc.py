@@ -58,7 +58,52 @@ def test_static_workspace_matches_allocating_entry_point_twice(types):
         rf = ref if types in (1, 3) else oracle.bits_to_f32(ref, bf16)
         rel = np.sqrt(((gf.astype(np.float64) - rf) ** 2).sum()) / np.sqrt((rf.astype(np.float64) ** 2).sum())
         assert rel <= 1e-3, f"call {call + 1}: relative Frobenius error {rel} against the CPU reference"
+    assert g.static_status() == 0  # the entry point's own device status word, not the allocating path's
     assert g.device_status() == 0
+
+
+@pytest.mark.parametrize("cfg,shape", [
+    (g.GemmConfig(256, 128, 4, 2, 4, 2), (512, 384, 2048 + 64, 0, 0, 0)),   # CTA pair + four K partitions
+    (g.GemmConfig(256, 512, 4, 2, 2, 0), (512, 1024, 1024, 0, 0, 1)),       # 512-wide pair tile, two partitions
+    (None, (16, 4096, 2048, 0, 0, 1)),                                      # skinny: operand swap, transposing epilogue
+    (g.GemmConfig(128, 128, 4, 1, 3, 0), (48, 2048, 1024, 0, 0, 0)),        # skinny with K partitions
+], ids=["pair-split4", "pair512-split2", "skinny-table", "skinny-split3"])
+def test_static_entry_point_shares_the_launch_rules(cfg, shape):
+    """The allocation-free entry point plans and launches exactly like the allocating one (CTA
+    pairs, 512-wide tiles, the operand swap of skinny problems), so their results are bit-equal."""
+    M, N, K, lc, la, lb = shape
+    L = g.loader()
+    A, B = oracle.init_matrix(M, K, la, True), oracle.init_matrix(K, N, lb, True)
+    want, got = _both(L, 3, A, B, M, N, K, lc, la, lb, cfg)
+    assert np.array_equal(want.view(np.uint32), got.view(np.uint32))
+    ref = oracle.hgemm(3, A, B, M, N, K, lc, la, lb)
+    check_parity(3, got, ref, K, 1.0 / 3.0, M, N, lc)
+    assert g.static_status() == 0
+
+
+def test_static_entry_point_allocates_nothing():
+    """The defining property: once the first call on the device has done its set-up, free device
+    memory is the same before and after any number of calls (the driver reports it per device,
+    so any cudaMalloc, stream-ordered allocation or growth of a cached buffer would show)."""
+    L = g.loader()
+    M, N, K = 128, 1024, 4096
+    A, B = _device(oracle.init_matrix(M, K, 0, False)), _device(oracle.init_matrix(K, N, 1, False))
+    C = torch.empty(M * N, dtype=torch.float32, device="cuda")
+
+    def calls():
+        for split in (8, 2, 5, 1):
+            cfg = g.GemmConfig(128, 128, 4, 1, split, 0)
+            L.gemm_static(C, A, B, M, N, K, 0, 0, 1, types=1, config=cfg)
+            L.gemm_static(C[: 16 * N], A, B, 16, N, K, 0, 0, 1, types=1)
+        torch.cuda.synchronize()
+
+    calls()  # first calls: the entry point's set-up, and the driver loads each kernel it meets
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        calls()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, f"free device memory changed by {free0 - free1} bytes"
+    assert g.static_status() == 0
 
 
 def test_static_entry_point_without_split_and_table_config():

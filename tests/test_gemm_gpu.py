@@ -50,7 +50,10 @@ def test_config1_known_answer():
 
 CONFIGS = [g.GemmConfig(128, 64, 8, 1, 1, 8), g.GemmConfig(128, 128, 6, 1, 1, 4), g.GemmConfig(128, 256, 4, 1, 1, 0),
            g.GemmConfig(256, 128, 8, 2, 1, 2), g.GemmConfig(256, 256, 6, 2, 1, 16), g.GemmConfig(128, 128, 2, 1, 1, 1),
-           g.GemmConfig(256, 256, 3, 2, 1, 1), g.GemmConfig(256, 512, 4, 2, 1, 16), g.GemmConfig(256, 512, 2, 2, 1, 3)]
+           g.GemmConfig(256, 256, 3, 2, 1, 1), g.GemmConfig(256, 512, 4, 2, 1, 16), g.GemmConfig(256, 512, 2, 2, 1, 3),
+           # snake raster (B200_GEMM_RASTER_SNAKE = 128 added to the band height): column sweep, ragged last band, one-row bands
+           g.GemmConfig(128, 64, 8, 1, 1, 128), g.GemmConfig(128, 128, 6, 1, 1, 128 + 2), g.GemmConfig(256, 256, 6, 2, 1, 128 + 1),
+           g.GemmConfig(256, 512, 4, 2, 1, 128 + 3)]
 
 
 @pytest.mark.parametrize("cfg", CONFIGS, ids=[f"m{c.tile_m}n{c.tile_n}s{c.stages}c{c.cluster}r{c.raster}" for c in CONFIGS])
@@ -59,7 +62,7 @@ def test_every_compiled_variant_every_layout(cfg):
     for types in range(4):
         bf16 = types >= 2
         for (la, lb, lc) in LAYOUTS:
-            for (M, N, K) in [(384, 1160, 192), (264, 136, 200)]:
+            for (M, N, K) in [(384, 1160, 192), (264, 136, 200)] + ([(904, 1160, 72)] if cfg.raster >= 128 else []):
                 A, B = seeded(M, N, K, la, lb, bf16)
                 ref = oracle.hgemm(types, A, B, M, N, K, lc, la, lb)
                 got = gpu_gemm(types, A, B, M, N, K, lc, la, lb, config=cfg)

@@ -344,6 +344,43 @@ def run_b200(args, rank, world, local_rank):
     value = flops_per_step * args.steps / (total_ms_max * 1e-3) / 1e12
 
     extra = {}
+    # ---- the vendor GEMM on the same GPU in the same run (N = 1): GPUs of this pool settle at
+    # different clocks under the 1 kW cap, so a sustained figure only means something next to the
+    # vendor library's on the same part ------------------------------------------------------------
+    if layouts and world == 1 and not args.no_vendor:
+        a2, b2 = A.view(M, K), B.view(N, K)
+        o2 = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        for _ in range(3):
+            torch.matmul(a2, b2.t(), out=o2)
+        torch.cuda.synchronize()
+        time.sleep(0.25)
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+        for k in range(4):
+            evs[k].record()
+            torch.matmul(a2, b2.t(), out=o2)
+        evs[4].record()
+        torch.cuda.synchronize()
+        v_burst = 2.0 * M * N * K / (min(evs[k].elapsed_time(evs[k + 1]) for k in range(4)) * 1e-3) / 1e12
+        n_v = 400  # warm the part up again, then ~1.5 s timed
+        for _ in range(n_v):
+            torch.matmul(a2, b2.t(), out=o2)
+        vs = ClockSampler(local_rank)
+        v0, v1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        vs.start()
+        v0.record()
+        for _ in range(4 * n_v):
+            torch.matmul(a2, b2.t(), out=o2)
+        v1.record()
+        torch.cuda.synchronize()
+        vclk = vs.stop()
+        v_ms = v0.elapsed_time(v1) / (4 * n_v)
+        extra["vendor_same_run"] = {"sustained": 2.0 * M * N * K / (v_ms * 1e-3) / 1e12, "burst": v_burst, "unit": "TFLOP/s",
+                                    "sm_mhz": vclk.get("sm_mhz"), "cycles_per_launch": v_ms * 1e-3 * vclk["sm_mhz"] * 1e6 if vclk.get("sm_mhz") else None,
+                                    "ratio_sustained": value / (2.0 * M * N * K / (v_ms * 1e-3) / 1e12),
+                                    "note": "torch.matmul bf16->bf16 8192^3 (vendor GEMM) on the same GPU right after the timed region: "
+                                            "best of 4 after 0.25 s idle, then 1600 calls back to back"}
+        del o2
     if world > 1 and wl["kind"] == "slab":
         extra.update(multi_gpu_extras(args, g, L, dist, dev, rank, world, wl, A, B, C, n_local, slab_of_b, barrier, value))
 
@@ -593,6 +630,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (profiling runs)")
+    ap.add_argument("--no-vendor", action="store_true", help="skip the vendor GEMM yardstick (profiling runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
     rank = int(os.environ.get("RANK", "0"))

@@ -16,7 +16,8 @@ CPP = os.path.join(ROOT, "tests", "cpp")
 
 
 def _run(binary):
-    env = dict(os.environ, ROCM_WMMA_GEMM_LIB_DIR=os.path.join(ROOT, "rocm_wmma_gemm_b200"))
+    pkg = os.path.join(ROOT, "rocm_wmma_gemm_b200")  # the loader dlopen()s librocm_wmma_gemm_sm100a.so by name
+    env = dict(os.environ, LD_LIBRARY_PATH=pkg + os.pathsep + os.environ.get("LD_LIBRARY_PATH", ""))
     return subprocess.run([binary], capture_output=True, text=True, timeout=900, env=env)
 
 

@@ -309,6 +309,47 @@ def consolidate(evaluate, table, shape, out):
     save_table(out, table)
 
 
+L2_BYTES = 126 << 20
+
+
+def traffic_raster(M, N, K, lc, cfg_dict, sms=148):
+    """Raster of a large problem chosen by DRAM traffic instead of by time.
+
+    For problems whose operands exceed L2 the timing of the raster values differs by less than
+    the run-to-run noise of a power-capped B200 (a search then keeps whatever value was lucky),
+    but the DRAM bytes differ by up to 30 % (hardware counters, 8192^3: column sweep 1.14 GB
+    read, bands of 16 tile-rows 0.87 GB, the same bands in snake order 0.84 GB).  The tiles in
+    flight at one time should cover a square of C (as many rows of A' as columns of B', in bytes),
+    and consecutive bands should meet at the same columns.  Returns None when the rule does
+    not apply (small problems stay as tuned)."""
+    mk, nk = (M, N) if lc == 0 else (N, M)
+    tile_m, tile_n = cfg_dict["tile_m"], cfg_dict["tile_n"]
+    if cfg_dict["split_k"] != 1 or tile_m < 256:
+        return None
+    if (mk + nk) * K * 2 < L2_BYTES:
+        return None
+    m_tiles, n_tiles = -(-mk // tile_m), -(-nk // tile_n)
+    units = sms // cfg_dict["cluster"]
+    if m_tiles * n_tiles < 2 * units:
+        return None
+    # band height b: b * tile_m rows of A' against (units / b) * tile_n columns of B'
+    best = min((1, 2, 4, 8, 16, 32), key=lambda b: abs(b * tile_m - units / b * tile_n))
+    best = min(best, m_tiles)
+    return RASTER_SNAKE + best
+
+
+def apply_traffic_raster(table) -> int:
+    """Rewrites the raster of every entry traffic_raster() covers; returns how many changed."""
+    changed = 0
+    for shape, per_layout in table.items():
+        for layout, e in per_layout.items():
+            r = traffic_raster(shape[0], shape[1], shape[2], layout[2], e["config"])
+            if r is not None and e["config"]["raster"] != r:
+                e["config"]["raster"] = r
+                changed += 1
+    return changed
+
+
 def main(argv=None):
     p = argparse.ArgumentParser(description="B200 GEMM tuner (parameter-less GOMEA)")
     p.add_argument("--input", "-i", help="existing JSON table: its entries seed the search and are kept")
@@ -323,11 +364,18 @@ def main(argv=None):
     p.add_argument("--evaluator", default="inprocess", choices=["inprocess", "subprocess"])
     p.add_argument("--tuner-binary", default=os.path.join(HERE, "tuner"))
     p.add_argument("--max-seconds", type=float, default=0, help="stop after this long (0 = no limit); the table is saved as it grows")
+    p.add_argument("--traffic-raster-only", action="store_true",
+                   help="no search: give the large entries of the input table the raster that minimises DRAM traffic, save, exit")
     args = p.parse_args(argv)
 
     group = "f32" if args.type in ("f32_f16", "f32_bf16") else "f16"
     out = args.output or os.path.join(HERE, f"gemm_config_sm100_{group}.json")
     table = load_table(args.input or out)
+    if args.traffic_raster_only:
+        n = apply_traffic_raster(table)
+        save_table(out, table)
+        print(f"raster set by the traffic rule in {n} entries; saved {out}")
+        return 0
     sizes = [tuple(int(x) for x in s.split(",")) for s in args.sizes] if args.sizes else DEFAULT_SIZES
 
     def lay(tok):
@@ -368,6 +416,8 @@ def main(argv=None):
             print(f"{M}x{N}x{K} A={'rc'[layout[0]]} B={'rc'[layout[1]]} C={'rc'[layout[2]]}: {to_dict(r['config'])} "
                   f"{r['time_ms']:.4f} ms {tflops:.0f} TFLOP/s ({r['evaluations']} evals)", flush=True)
         consolidate(evaluate, table, shape, out)
+    apply_traffic_raster(table)
+    save_table(out, table)
     print("saved", out)
     return 0
 

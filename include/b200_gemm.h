@@ -100,7 +100,11 @@ enum b200_gemm_types {
  *   stages   depth of the TMA -> shared-memory ring (2 .. 12, clamped to what fits; kernels
  *            that stage several k-blocks per ring slot size the ring themselves)
  *   cluster  1 = one CTA per tile, 2 = a CTA pair shares one tile (cta_group::2 MMA)
- *   split_k  number of K partitions reduced through an f32 workspace (1 = none)
+ *   split_k  number of K partitions reduced through an f32 workspace (1 = none).  0 selects the
+ *            balanced schedule (stream-K, the reference's roadmap item README.md:202): the K
+ *            loops of all tiles are laid end to end and cut into one equal run per SM, so every
+ *            SM does the same number of K steps whatever the tile count; partial tiles meet in
+ *            a deterministic fix-up pass.  Needs tile_n <= 256 and N % 4 == 0 in the kernel view.
  *   raster   tile-rows per raster band (the reference's `swizzle` key,
  *            rocm_wmma_gemm/include/rocm_wmma_gemm/kernel/mapping.hpp:108-287); 0 = column sweep.
  *            Adding B200_GEMM_RASTER_SNAKE selects the boustrophedon order of the reference's

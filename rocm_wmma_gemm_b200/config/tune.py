@@ -44,7 +44,7 @@ SPACE = {
     "tile_m": [128, 256],
     "tile_n": [64, 128, 160, 192, 224, 256, 512],   # 160 / 192 / 224: run-time widths of the 256-column pair kernel
     "stages": [2, 3, 4, 6, 8, 12],
-    "split_k": [1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 12, 14, 16, 24, 32],
+    "split_k": [0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 12, 14, 16, 24, 32],   # 0: balanced (stream-K) schedule
     # band height in tile-rows (0 = column sweep); + RASTER_SNAKE: every other band backwards
     "raster": [0, 1, 2, 4, 8, 16, 32, 128, 130, 132, 136, 144, 160],
 }
@@ -97,7 +97,9 @@ def check_constraints(cfg, M=None, N=None, K=None, lc=0) -> bool:
         return False                      # each CTA of a pair stages >= 64 rows of B
     if stages > max_stages(tile_n, cl):
         return False                      # ring + epilogue staging must fit 227 KiB
-    if K is not None:
+    if split_k == 0 and tile_n > 256:
+        return False                      # the balanced schedule runs on tiles of up to 256 columns
+    if K is not None and split_k > 0:
         k_blocks = (K + 63) // 64
         if split_k > k_blocks:
             return False

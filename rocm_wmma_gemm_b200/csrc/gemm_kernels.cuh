@@ -58,6 +58,10 @@ struct GemmParams {
     uint32_t k4d;          // one-CTA kernels: K-major operands use the 4-D (chunked K) maps
     uint32_t snake;        // raster: odd bands (odd columns of a column sweep) run backwards
     uint32_t l2_hints;     // L2 eviction priorities: bits [0,2) A', [2,4) B', [4,6) D (L2_HINT_*)
+    uint32_t balanced;     // 1: balanced (stream-K) schedule, see WorkCursor; outputs are f32 partial tiles
+    uint32_t units_per_tile; // balanced: K steps (ring slots of kc k-blocks) per tile
+    uint32_t workers;      // balanced: runs the work is cut into (= persistent CTAs / CTA pairs)
+    uint32_t total_units;  // balanced: tiles x units_per_tile
     uint32_t ndst;         // gathering kernels: number of destination matrices every tile is stored to
     uint32_t dst_row0;     // gathering kernels: row and column of D(0, 0) within each destination
     uint32_t dst_col0;
@@ -183,19 +187,14 @@ struct WorkCoord {
     uint32_t kb0, kb1; // k-block range
 };
 
-__device__ __forceinline__ WorkCoord decode_work(const GemmParams& p, uint32_t w, int bn, int bm)
+// Tile index -> (tile-row, tile-column) under the problem's raster.
+// Raster (the reference's tile_mapper, kernel/mapping.hpp:108-287): tiles are walked in bands
+// of group_m tile-rows, tile-rows fastest, so that the tiles in flight share a panel of A'
+// and a few panels of B' in L2.  With `snake` every other band runs its columns backwards
+// (and every other column its rows): the first tiles of a band reuse the B' panels the last
+// tiles of the band before it have just read.
+__device__ __forceinline__ void tile_coords(const GemmParams& p, uint32_t t, uint32_t& m_idx, uint32_t& n_idx)
 {
-    const uint32_t tiles = p.m_tiles * p.n_tiles;
-    const uint32_t t     = w % tiles;
-    const uint32_t r     = w / tiles;
-    const uint32_t split = r % p.split_k;
-    const uint32_t b     = r / p.split_k;
-    uint32_t       m_idx, n_idx;
-    // Raster (the reference's tile_mapper, kernel/mapping.hpp:108-287): tiles are walked in bands
-    // of group_m tile-rows, tile-rows fastest, so that the tiles in flight share a panel of A'
-    // and a few panels of B' in L2.  With `snake` every other band runs its columns backwards
-    // (and every other column its rows): the first tiles of a band reuse the B' panels the last
-    // tiles of the band before it have just read.
     if (p.group_m == 0u) {
         m_idx = t % p.m_tiles;
         n_idx = t / p.m_tiles;
@@ -214,6 +213,17 @@ __device__ __forceinline__ WorkCoord decode_work(const GemmParams& p, uint32_t w
         }
         m_idx = first_m + m_in;
     }
+}
+
+__device__ __forceinline__ WorkCoord decode_work(const GemmParams& p, uint32_t w, int bn, int bm)
+{
+    const uint32_t tiles = p.m_tiles * p.n_tiles;
+    const uint32_t t     = w % tiles;
+    const uint32_t r     = w / tiles;
+    const uint32_t split = r % p.split_k;
+    const uint32_t b     = r / p.split_k;
+    uint32_t       m_idx, n_idx;
+    tile_coords(p, t, m_idx, n_idx);
     WorkCoord c;
     c.m0    = m_idx * static_cast<uint32_t>(bm);
     c.n0    = n_idx * static_cast<uint32_t>(bn);
@@ -222,6 +232,71 @@ __device__ __forceinline__ WorkCoord decode_work(const GemmParams& p, uint32_t w
     c.kb0   = split * p.kb_per_split;
     c.kb1   = min(p.k_blocks, c.kb0 + p.kb_per_split);
     return c;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Work of one persistent worker (a CTA, or a CTA pair).
+//
+// Plain schedule: work items unit, unit + units, ... of the num_work (batch x K partition x
+// tile) items.
+//
+// Balanced schedule (stream-K; the reference's roadmap names it, README.md:202): the tiles'
+// K loops are laid end to end - tile 0's K steps, then tile 1's, ... - and that line of
+// total_units steps is cut into `workers` equal runs, one per worker, wherever the cuts fall.
+// A worker walks its run segment by segment (a segment = the part of one tile's K loop inside
+// the run), so every SM gets the same number of K steps whatever the tile count.  Every segment
+// leaves an f32 partial tile in the workspace at slot (tile + worker) - along the line either
+// the tile or the worker advances from one segment to the next, so the sum is unique - and the
+// fix-up pass (streamk_reduce_kernel) adds a tile's partials in K order.  No CTA waits for
+// another.
+// ---------------------------------------------------------------------------------------------
+struct WorkCursor {
+    uint32_t next;  // plain: next work item; balanced: next K step of the run
+    uint32_t end;   // balanced: end of the run
+};
+
+__device__ __forceinline__ uint32_t run_start(const GemmParams& p, uint32_t worker)
+{
+    return static_cast<uint32_t>(static_cast<uint64_t>(worker) * p.total_units / p.workers);
+}
+
+__device__ __forceinline__ WorkCursor work_begin(const GemmParams& p, uint32_t unit)
+{
+    WorkCursor cur;
+    if (p.balanced) {
+        cur.next = run_start(p, unit);
+        cur.end  = run_start(p, unit + 1u);
+    } else {
+        cur.next = unit;
+        cur.end  = p.num_work;
+    }
+    return cur;
+}
+
+// Next piece of work of this worker; false when there is none left.
+__device__ __forceinline__ bool work_next(const GemmParams& p, WorkCursor& cur, uint32_t unit, uint32_t units,
+                                          int bn, int bm, WorkCoord& c)
+{
+    if (cur.next >= cur.end) return false;
+    if (!p.balanced) {
+        c = decode_work(p, cur.next, bn, bm);
+        cur.next += units;
+        return true;
+    }
+    const uint32_t tile  = cur.next / p.units_per_tile;          // over batch x tiles
+    const uint32_t first = cur.next - tile * p.units_per_tile;   // first K step of the segment within the tile
+    const uint32_t last  = min(p.units_per_tile, first + (cur.end - cur.next));
+    const uint32_t tiles = p.m_tiles * p.n_tiles;
+    uint32_t       m_idx, n_idx;
+    tile_coords(p, tile % tiles, m_idx, n_idx);
+    c.m0    = m_idx * static_cast<uint32_t>(bm);
+    c.n0    = n_idx * static_cast<uint32_t>(bn);
+    c.z_in  = tile / tiles;
+    c.z_out = tile + unit; // workspace slot of this segment's partial tile
+    c.kb0   = first * p.kc;
+    c.kb1   = min(p.k_blocks, last * p.kc);
+    cur.next += last - first;
+    return true;
 }
 
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
@@ -437,8 +512,9 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
             bool     ok = true;
             const uint64_t pol_a = ptx::make_l2_policy(p.l2_hints & 3u);
             const uint64_t pol_b = ptx::make_l2_policy((p.l2_hints >> 2) & 3u);
-            for (uint32_t w = unit; ok && w < p.num_work; w += units) {
-                const WorkCoord c  = decode_work(p, w, wn, tile_m);
+            WorkCursor cur = work_begin(p, unit);
+            WorkCoord  c;
+            for (uint32_t w = unit; ok && work_next(p, cur, unit, units, wn, tile_m, c); w += units) {
                 const int32_t   am = static_cast<int32_t>(c.m0 + rank * BLOCK_M);
                 const int32_t   bn = static_cast<int32_t>(c.n0 + rank * sub_rows);
                 // Streaming (HBM-bound) problems rotate each work unit's K order so that the CTAs
@@ -570,8 +646,9 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
             const uint32_t b_kstep = p.b_mn_major ? (2u * 1024u) >> 4 : (UMMA_K * 2u) >> 4;
             uint32_t       stage = 0, phase = 0, it = 0;
             bool           ok = true;
-            for (uint32_t w = unit; ok && w < p.num_work; w += units, ++it) {
-                const WorkCoord c = decode_work(p, w, wn, tile_m);
+            WorkCursor cur = work_begin(p, unit);
+            WorkCoord  c;
+            for (; ok && work_next(p, cur, unit, units, wn, tile_m, c); ++it) {
                 if constexpr (NSUB == 2) {
                     // Two column halves with their own full / empty barriers (s_tfull[h],
                     // s_tempty[h]), staggered by stg_x k-blocks: see TileStep.  Three
@@ -709,8 +786,9 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
         uint32_t       it   = 0, nstore = 0;
         bool           ok   = true;
         const uint64_t pol_d = ptx::make_l2_policy((p.l2_hints >> 4) & 3u);
-        for (uint32_t w = unit; ok && w < p.num_work; w += units, ++it) {
-            const WorkCoord c      = decode_work(p, w, wn, tile_m);
+        WorkCursor cur = work_begin(p, unit);
+        WorkCoord  c;
+        for (; ok && work_next(p, cur, unit, units, wn, tile_m, c); ++it) {
             const uint32_t  buf    = it % NUM_ACC;
             const uint32_t  aphase = (it / NUM_ACC) & 1u;
             // A 512-wide tile is drained as two 256-column halves, each published (s_tfull[h])
@@ -824,6 +902,9 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                             // output happens tile by tile under the main loop of the next tile.
                             for (uint32_t d = 0; d < p.ndst; ++d)
                                 ptx::tma_store_3d(&tmDs[d], sbuf, col0 + p.dst_col0, row0 + p.dst_row0, c.z_out, pol_d);
+                        } else if (p.balanced) {
+                            // partial tile: tile-local coordinates, one workspace slot per segment
+                            ptx::tma_store_3d(&tmD, sbuf, col0 - c.n0, row0 - c.m0, c.z_out, pol_d);
                         } else {
                             ptx::tma_store_3d(&tmD, sbuf, col0, row0, c.z_out, pol_d);
                         }
@@ -915,6 +996,75 @@ __global__ void __launch_bounds__(256)
             u.x = *reinterpret_cast<const uint32_t*>(&a);
             u.y = *reinterpret_cast<const uint32_t*>(&b);
             reinterpret_cast<uint2*>(out)[i] = u;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Fix-up pass of the balanced (stream-K) schedule: out(tile) = convert(sum of the tile's partial
+// tiles), partials added in K order (ascending worker), so the result does not depend on timing.
+// `ws` holds one dense tile_m x tile_n f32 tile per slot; tile t's partials are the slots
+// t + w for the workers w whose runs overlap the tile's K steps (see WorkCursor).  One block
+// handles 32 rows of one tile per step; N is a multiple of 4, so a float4 never straddles the
+// matrix edge.  HBM/L2-bound: (parts x 4 + sizeof(out)) bytes per element.
+// ---------------------------------------------------------------------------------------------
+template <int OUT>
+__global__ void __launch_bounds__(256)
+    streamk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ out, const GemmParams p, uint32_t tile_m,
+                          uint32_t tile_n)
+{
+    const uint32_t groups   = tile_m / 32u;
+    const uint32_t tiles    = p.m_tiles * p.n_tiles;
+    const uint32_t jobs     = tiles * p.batch * groups;
+    const uint32_t row4     = tile_n / 4u; // float4 per tile row
+    const uint64_t tile_sz4 = static_cast<uint64_t>(tile_m) * row4;
+    ptx::grid_dep_wait(); // the partials are complete once the GEMM grid before this one has finished
+    ptx::grid_dep_launch();
+    for (uint32_t job = blockIdx.x; job < jobs; job += gridDim.x) {
+        const uint32_t tile = job / groups; // over batch x tiles
+        const uint32_t g    = job - tile * groups;
+        // workers whose runs hold the tile's first and last K step
+        const uint64_t x0 = static_cast<uint64_t>(tile) * p.units_per_tile, x1 = x0 + p.units_per_tile - 1u;
+        const uint32_t w0 = static_cast<uint32_t>(((x0 + 1u) * p.workers + p.total_units - 1u) / p.total_units) - 1u;
+        const uint32_t w1 = static_cast<uint32_t>(((x1 + 1u) * p.workers + p.total_units - 1u) / p.total_units) - 1u;
+        uint32_t       m_idx, n_idx;
+        tile_coords(p, tile % tiles, m_idx, n_idx);
+        const uint32_t z  = tile / tiles;
+        const uint32_t m0 = m_idx * tile_m + g * 32u, n0 = n_idx * tile_n;
+        if (m0 >= p.M) continue;
+        const float4* base = reinterpret_cast<const float4*>(ws) + static_cast<uint64_t>(g) * 32u * row4;
+        for (uint32_t idx = threadIdx.x; idx < 32u * row4; idx += blockDim.x) {
+            const uint32_t rr = idx / row4, c4 = idx - rr * row4;
+            const uint32_t row = m0 + rr, col = n0 + c4 * 4u;
+            if (row >= p.M || col >= p.N) continue;
+            const float4* src = base + static_cast<uint64_t>(tile + w0) * tile_sz4 + idx;
+            float4        acc = __ldg(src);
+            for (uint32_t w = w0 + 1u; w <= w1; ++w) {
+                src += tile_sz4;
+                const float4 t = __ldg(src);
+                acc.x += t.x;
+                acc.y += t.y;
+                acc.z += t.z;
+                acc.w += t.w;
+            }
+            const uint64_t at = (static_cast<uint64_t>(z) * p.M + row) * p.N + col; // element index; col % 4 == 0
+            if constexpr (OUT == OUT_F32) {
+                *reinterpret_cast<float4*>(static_cast<float*>(out) + at) = acc;
+            } else if constexpr (OUT == OUT_F16) {
+                const __half2 a = __floats2half2_rn(acc.x, acc.y);
+                const __half2 b = __floats2half2_rn(acc.z, acc.w);
+                uint2         u;
+                u.x = *reinterpret_cast<const uint32_t*>(&a);
+                u.y = *reinterpret_cast<const uint32_t*>(&b);
+                *reinterpret_cast<uint2*>(static_cast<__half*>(out) + at) = u;
+            } else {
+                const __nv_bfloat162 a = __floats2bfloat162_rn(acc.x, acc.y);
+                const __nv_bfloat162 b = __floats2bfloat162_rn(acc.z, acc.w);
+                uint2                u;
+                u.x = *reinterpret_cast<const uint32_t*>(&a);
+                u.y = *reinterpret_cast<const uint32_t*>(&b);
+                *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(out) + at) = u;
+            }
         }
     }
 }

@@ -465,7 +465,7 @@ static int check_config(const b200_gemm_config& c)
     if (c.cluster == 2 && c.tile_n == 64) return fail(B200_GEMM_ERR_BAD_CONFIG, "tile_n 64 needs cluster 1");
     if (c.cluster == 1 && c.tile_n == 512) return fail(B200_GEMM_ERR_BAD_CONFIG, "tile_n 512 needs cluster 2");
     if (c.stages < 2 || c.stages > MAX_STAGES) return fail(B200_GEMM_ERR_BAD_CONFIG, "stages %d outside 2..%d", c.stages, MAX_STAGES);
-    if (c.split_k < 1 || c.split_k > 64) return fail(B200_GEMM_ERR_BAD_CONFIG, "split_k %d outside 1..64", c.split_k);
+    if (c.split_k < 0 || c.split_k > 64) return fail(B200_GEMM_ERR_BAD_CONFIG, "split_k %d outside 0..64 (0 = balanced schedule)", c.split_k);
     if (c.raster < 0 || (c.raster & ~B200_GEMM_RASTER_SNAKE) > 64)
         return fail(B200_GEMM_ERR_BAD_CONFIG, "raster %d: band height outside 0..64 (add %d for the snake order)", c.raster,
                     B200_GEMM_RASTER_SNAKE);
@@ -742,6 +742,28 @@ static cudaError_t launch_reduce(int out, unsigned blocks, cudaStream_t s, const
     }
 }
 
+// Fix-up pass of the balanced schedule, a programmatic dependent of the GEMM kernel like the
+// split-K reduction.
+static cudaError_t launch_streamk_reduce(int out, unsigned blocks, cudaStream_t s, const float* ws, void* d, const GemmParams& gp,
+                                         uint32_t tile_m, uint32_t tile_n)
+{
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim            = dim3(blocks);
+    lc.blockDim           = dim3(256);
+    lc.dynamicSmemBytes   = 0;
+    lc.stream             = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs                                           = attr;
+    lc.numAttrs                                        = 1;
+    switch (out) {
+        case OUT_F32: return cudaLaunchKernelEx(&lc, streamk_reduce_kernel<OUT_F32>, ws, d, gp, tile_m, tile_n);
+        case OUT_F16: return cudaLaunchKernelEx(&lc, streamk_reduce_kernel<OUT_F16>, ws, d, gp, tile_m, tile_n);
+        default: return cudaLaunchKernelEx(&lc, streamk_reduce_kernel<OUT_BF16>, ws, d, gp, tile_m, tile_n);
+    }
+}
+
 // Everything the launch path decides before it touches the GPU.
 struct LaunchPlan {
     bool             generic    = false; // TMA cannot address the problem: CUDA-core kernel
@@ -749,6 +771,7 @@ struct LaunchPlan {
     bool             narrow     = false; // kernel view of at most 64 columns (or transposed)
     bool             slot       = false; // one-CTA kernel with kc k-blocks per ring slot
     bool             k4d        = false; // K-major operands through the 4-D (chunked K) maps
+    bool             balanced   = false; // balanced (stream-K) schedule: runs of K steps cut across tiles
     View             v{};
     b200_gemm_config cfg{};
     uint32_t         bm = BLOCK_M, kc = 1, kb_per_split = 0;
@@ -763,8 +786,15 @@ static int make_plan(const Problem& p, const b200_gemm_config* user_cfg, int sm_
     // so when the kernel view has few rows and many columns the operands swap roles once more
     // (the kernel computes D^T) and the epilogue writes D^T transposed, i.e. D.  No 128-row
     // tile of mostly zero-filled A' is staged and the ring holds twice as many slots.
+    bool              tuned = true;
+    b200_gemm_config& cfg   = pl.cfg;
+    cfg                     = resolve_config(p, user_cfg, nullptr, &tuned);
+    int st                  = check_config(cfg);
+    if (st != B200_GEMM_OK) return st;
+    // split_k == 0 asks for the balanced (stream-K) schedule, which keeps the plain orientation.
+    bool  balanced   = cfg.split_k == 0;
     bool& transposed = pl.transposed;
-    if (v.M <= 64 && v.N >= 128 && operands_tma_ok(p, v) && reinterpret_cast<uintptr_t>(v.d) % 16 == 0 &&
+    if (!balanced && v.M <= 64 && v.N >= 128 && operands_tma_ok(p, v) && reinterpret_cast<uintptr_t>(v.d) % 16 == 0 &&
         ((size_t)v.M * v.N) % 4 == 0) {
         std::swap(v.a, v.b);
         std::swap(v.M, v.N);
@@ -777,12 +807,7 @@ static int make_plan(const Problem& p, const b200_gemm_config* user_cfg, int sm_
         return B200_GEMM_OK;
     }
 
-    bool              tuned = true;
-    b200_gemm_config& cfg   = pl.cfg;
-    cfg                     = resolve_config(p, user_cfg, nullptr, &tuned);
-    int st                  = check_config(cfg);
-    if (st != B200_GEMM_OK) return st;
-    if (!tuned) adapt_config(cfg, v, p.batch, sm_count);
+    if (!tuned && !balanced) adapt_config(cfg, v, p.batch, sm_count);
     // Narrow kernel views (at most 64 columns) run on the narrow one-CTA variants whatever
     // tile the table names: tile_n is the smallest compiled width that covers N (an MN-major
     // B' is loaded in 64-row boxes, so it needs 64) and the ring is as deep as fits.
@@ -813,8 +838,18 @@ static int make_plan(const Problem& p, const b200_gemm_config* user_cfg, int sm_
     // The narrow staged-epilogue tiles (a skinny problem with a column-major C) stream the large
     // operand the same way; their epilogue stores whole 32-row groups, so their slabs are
     // multiples of 32 rows.
+    // The balanced schedule lays the tiles' K loops end to end and cuts that line into equal runs,
+    // one per SM (WorkCursor in gemm_kernels.cuh).  It runs on the tiles of up to 256 columns and
+    // its fix-up pass works in float4 units.
+    if (balanced && (cfg.tile_n > 256 || v.N % 4)) {
+        if (user_cfg)
+            return fail(B200_GEMM_ERR_BAD_CONFIG, "the balanced schedule (split_k 0) needs tile_n <= 256 and N %% 4 == 0 in the kernel view");
+        balanced = false;
+    }
+    if (cfg.split_k == 0) cfg.split_k = 1; // no per-tile K partitions either way
+    pl.balanced = balanced;
     uint32_t& bm = pl.bm;
-    if (narrow && !user_cfg && (transposed || !v.a_mn)) { // (staged tiles on an M-major operand: measured slower)
+    if (narrow && !user_cfg && !balanced && (transposed || !v.a_mn)) { // (staged tiles on an M-major operand: measured slower)
         const uint32_t sms       = (uint32_t)sm_count;
         const uint32_t step      = v.a_mn ? 64u : (transposed ? 8u : 32u);
         uint64_t       best_cost = ~0ull;
@@ -941,7 +976,7 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
         return fail(B200_GEMM_ERR_MISALIGNED,
                     "the allocation-free entry point needs 16-byte aligned pointers and contiguous extents that are "
                     "multiples of 8 elements (M=%zu N=%zu K=%zu)", p.M, p.N, p.K);
-    if (gather && (pl.generic || pl.transposed || pl.cfg.split_k != 1 || pl.cfg.cluster != 2 || pl.cfg.tile_n < 256 ||
+    if (gather && (pl.generic || pl.transposed || pl.balanced || pl.cfg.split_k != 1 || pl.cfg.cluster != 2 || pl.cfg.tile_n < 256 ||
                    p.batch != 1))
         return fail(B200_GEMM_ERR_BAD_CONFIG,
                     "the fused gather needs a plan on the 256-row pair tiles without K partitions (got %s, tile_n %d, cluster %d, "
@@ -967,6 +1002,7 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
     const uint32_t          bm           = pl.bm;
     const uint32_t          kc           = pl.kc;
     const uint32_t          kb_per_split = pl.kb_per_split;
+    const bool              balanced     = pl.balanced;
 
     const int      bn   = cfg.tile_n;
     const int      out  = out_kind(p.types);
@@ -993,6 +1029,18 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
     const uint64_t work = (uint64_t)gp.batch * split * gp.m_tiles * gp.n_tiles;
     if (work > 0x7fffffffull) return fail(B200_GEMM_ERR_BAD_SIZE, "too many tiles (%llu)", (unsigned long long)work);
     gp.num_work   = (uint32_t)work;
+    // Balanced schedule: `work` tiles of units_per_tile K steps each, cut into `workers` runs.
+    const uint32_t tile_rows = slot ? bm : (uint32_t)BLOCK_M * cl;
+    gp.balanced = gp.units_per_tile = gp.workers = gp.total_units = 0;
+    if (balanced) {
+        const uint64_t upt   = (gp.k_blocks + kc - 1) / kc;
+        const uint64_t total = work * upt;
+        if (total > 0x7fffffffull) return fail(B200_GEMM_ERR_BAD_SIZE, "too many K steps for the balanced schedule (%llu)", (unsigned long long)total);
+        gp.balanced       = 1;
+        gp.units_per_tile = (uint32_t)upt;
+        gp.total_units    = (uint32_t)total;
+        gp.workers        = (uint32_t)std::min<uint64_t>(total, (uint64_t)env.sm_count / cl);
+    }
     const int umma_n = bn > 256 ? 256 : bn; // columns per MMA; a 512-wide tile is two sub-tiles
     gp.a_mn_major = v.a_mn ? 1u : 0u;
     gp.b_mn_major = v.b_mn ? 1u : 0u;
@@ -1022,9 +1070,12 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
 
     // Split-K partials go to this stream's cached f32 workspace, laid out [batch][split][Mk][Nk].
     float*       ws       = nullptr;
-    const size_t ws_bytes = split > 1 ? (size_t)p.batch * split * v.M * v.N * sizeof(float) : 0;
+    // (balanced: one tile_rows x bn partial tile per segment, slots tile + worker)
+    const size_t ws_slots = balanced ? (size_t)work + gp.workers : 0;
+    const size_t ws_bytes = balanced ? ws_slots * tile_rows * bn * sizeof(float)
+                                     : (split > 1 ? (size_t)p.batch * split * v.M * v.N * sizeof(float) : 0);
     bool         ws_stream_ordered = false;
-    if (split > 1) {
+    if (split > 1 || balanced) {
         if (!transposed && v.N % 4) return fail(B200_GEMM_ERR_BAD_CONFIG, "split_k needs N %% 4 == 0 in the kernel view");
         if (fixed) {
             if (ws_bytes > env.fixed_ws_bytes)
@@ -1060,7 +1111,9 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
         tmD    = tmA; // not used by the transposed epilogue; any valid descriptor will do
         gp.out = split > 1 ? static_cast<void*>(ws) : v.d;
     } else if (st == B200_GEMM_OK) {
-        if (split > 1)
+        if (balanced)
+            st = encode_map(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ws, (uint64_t)bn, tile_rows, ws_slots, 32, 32);
+        else if (split > 1)
             st = encode_map(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ws, v.N, v.M, (uint64_t)p.batch * split, 32, 32);
         else if (out == OUT_F32)
             st = encode_map(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, v.d, v.N, v.M, p.batch, 32, 32);
@@ -1094,8 +1147,8 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
 
     const uint32_t smem     = transposed ? slab_smem_bytes((int)bm, bn, (int)kc, cfg.stages)
                               : (slot ? slot_smem_bytes(bn, (int)kc, cfg.stages) : gemm_smem_bytes(compiled_width(bn), (int)cl, cfg.stages));
-    const uint32_t units    = std::min<uint32_t>(gp.num_work, (uint32_t)env.sm_count / cl);
-    const int      kern_out = split > 1 ? OUT_F32 : out;
+    const uint32_t units    = balanced ? gp.workers : std::min<uint32_t>(gp.num_work, (uint32_t)env.sm_count / cl);
+    const int      kern_out = (split > 1 || balanced) ? OUT_F32 : out;
     cudaError_t    e;
     if (transposed) {
         switch (bn) {
@@ -1124,7 +1177,14 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
                     cfg.stages, smem);
     }
 
-    if (split > 1) {
+    if (balanced) {
+        const uint64_t jobs   = work * (tile_rows / 32u);
+        const unsigned blocks = (unsigned)std::min<uint64_t>(jobs, (uint64_t)env.sm_count * 8);
+        e = launch_streamk_reduce(out, blocks, stream, ws, v.d, gp, tile_rows, (uint32_t)bn);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        if (ws_stream_ordered) cudaFreeAsync(ws, stream);
+        if (e != cudaSuccess) return fail(B200_GEMM_ERR_CUDA, "balanced-schedule fix-up launch failed: %s", cudaGetErrorString(e));
+    } else if (split > 1) {
         const uint64_t mn     = (uint64_t)v.M * v.N;
         const uint64_t total4 = mn * p.batch / 4;
         const unsigned blocks = (unsigned)std::min<uint64_t>((total4 + 255) / 256, (uint64_t)env.sm_count * 8);
@@ -1301,6 +1361,14 @@ extern "C" size_t b200_gemm_workspace_bytes(int types, size_t M, size_t N, size_
     const Problem p = planning_problem(types, M, N, K, batch_count, layout_c, layout_a, layout_b);
     LaunchPlan    pl;
     if (make_plan(p, user, planning_sm_count(0), &pl) != B200_GEMM_OK || pl.generic) return 0;
+    if (pl.balanced) {
+        const uint32_t cl      = (uint32_t)pl.cfg.cluster;
+        const uint32_t tile_m  = pl.slot ? pl.bm : (uint32_t)BLOCK_M * cl;
+        const uint64_t tiles   = (uint64_t)((pl.v.M + tile_m - 1) / tile_m) * ((pl.v.N + pl.cfg.tile_n - 1) / pl.cfg.tile_n) * batch_count;
+        const uint64_t upt     = ((pl.v.K + BLOCK_K - 1) / BLOCK_K + pl.kc - 1) / pl.kc;
+        const uint64_t workers = std::min<uint64_t>(tiles * upt, (uint64_t)planning_sm_count(0) / cl);
+        return (size_t)(tiles + workers) * tile_m * pl.cfg.tile_n * sizeof(float);
+    }
     return pl.cfg.split_k > 1 ? batch_count * (size_t)pl.cfg.split_k * M * N * sizeof(float) : 0;
 }
 
@@ -1331,11 +1399,12 @@ extern "C" int b200_gemm_plan(int types, size_t M, size_t N, size_t K, size_t ba
     out->tile_m            = (int)tile_m;
     out->tile_n            = pl.cfg.tile_n;
     out->cluster           = pl.cfg.cluster;
-    out->split_k           = pl.cfg.split_k;
+    out->split_k           = pl.balanced ? 0 : pl.cfg.split_k;
     out->slots             = pl.cfg.stages;
     out->k_blocks_per_slot = (int)pl.kc;
     out->raster            = pl.cfg.raster;
-    out->ctas              = (int)(cl * std::min<uint64_t>(work, (uint64_t)sms / cl));
+    const uint64_t k_steps = pl.balanced ? work * ((((uint64_t)pl.v.K + BLOCK_K - 1) / BLOCK_K + pl.kc - 1) / pl.kc) : work;
+    out->ctas              = (int)(cl * std::min<uint64_t>(k_steps, (uint64_t)sms / cl));
     out->work_units        = (long long)work;
     return B200_GEMM_OK;
 }

@@ -139,6 +139,56 @@ def test_split_k(split_k):
             assert np.array_equal(got.view(np.uint8), again.view(np.uint8)), "split-K must be deterministic"
 
 
+BALANCED = [
+    # tile_m, tile_n, cluster | M, N, K: tiles x K steps that do not divide by the SM count
+    (128, 256, 1, 128, 8192, 2048),    # skinny: 32 tiles cut into 148 runs, 4-5 runs per tile
+    (128, 128, 1, 384, 1160, 1280 + 64),  # ragged N and K, two k-blocks per ring slot
+    (128, 64, 1, 264, 136, 4096),      # narrow one-CTA tile, four k-blocks per slot
+    (256, 256, 2, 2048, 2048, 512),    # CTA pairs: 64 tiles on 74 pairs
+    (256, 128, 2, 520, 1000, 1024),    # CTA pairs, ragged everywhere
+    (256, 192, 2, 640, 1184, 448),     # run-time tile width (K-major B' layouts only)
+    (128, 256, 1, 64, 4096, 8192),     # 64 rows without the operand swap
+]
+
+
+@pytest.mark.parametrize("tile_m,tile_n,cluster,M,N,K", BALANCED, ids=[f"{b[0]}x{b[1]}-{b[3]}x{b[4]}x{b[5]}" for b in BALANCED])
+def test_balanced_schedule(tile_m, tile_n, cluster, M, N, K):
+    """split_k = 0: the tiles' K loops laid end to end and cut into one equal run per SM
+    (stream-K); partial tiles meet in the fix-up pass.  All type pairs and layouts, bit-identical
+    from run to run, and the same numbers as the plain schedule up to the order of the f32 sum."""
+    for types in range(4):
+        bf16 = types >= 2
+        for (la, lb, lc) in LAYOUTS:
+            cfg = g.GemmConfig(tile_m, tile_n, 4, cluster, 0, 2)
+            A, B = seeded(M, N, K, la, lb, bf16)
+            flex = tile_n not in (64, 128, 256)
+            b_n_major = (lb == 0) if lc == 0 else (la == 1)  # kernel view: is B' N-major?
+            chunk = 32 if types in (1, 3) else 64
+            if flex and (b_n_major or tile_n % chunk):
+                with pytest.raises(g.GemmError):
+                    gpu_gemm(types, A, B, M, N, K, lc, la, lb, config=cfg)
+                continue
+            ref = oracle.hgemm(types, A, B, M, N, K, lc, la, lb)
+            got = gpu_gemm(types, A, B, M, N, K, lc, la, lb, config=cfg)
+            check_parity(types, got, ref, K, SIGMA_UNIFORM, M, N, lc)
+            if (la, lb, lc) in ((0, 1, 0), (1, 0, 1)):
+                again = gpu_gemm(types, A, B, M, N, K, lc, la, lb, config=cfg)
+                assert np.array_equal(got.view(np.uint8), again.view(np.uint8)), "the balanced schedule must be deterministic"
+
+
+def test_balanced_schedule_batched_and_rejected():
+    M, N, K, batch = 192, 320, 1024, 3
+    A = np.concatenate([oracle.init_matrix(M, K, 0, True)[(np.arange(M * K) + 97 * b) % (M * K)] for b in range(batch)])
+    B = np.concatenate([oracle.init_matrix(K, N, 1, True)[(np.arange(K * N) + 31 * b) % (K * N)] for b in range(batch)])
+    got = gpu_gemm(3, A, B, M, N, K, 0, 0, 1, batch=batch, config=g.GemmConfig(128, 128, 4, 1, 0, 0))
+    for b in range(batch):
+        ref = oracle.hgemm(3, A[b * M * K:(b + 1) * M * K], B[b * K * N:(b + 1) * K * N], M, N, K, 0, 0, 1)
+        check_parity(3, got[b * M * N:(b + 1) * M * N], ref, K, SIGMA_UNIFORM, M, N, 0)
+    # the 512-wide tile has no balanced form
+    with pytest.raises(g.GemmError):
+        gpu_gemm(3, A[: M * K], B[: K * N], M, N, K, 0, 0, 1, config=g.GemmConfig(256, 512, 4, 2, 0, 0))
+
+
 def test_all_layouts_agree():
     """The same logical product through all 8 layouts gives the same C (tight tolerance: the
     products are identical, only tile shapes and operand roles differ)."""

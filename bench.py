@@ -46,7 +46,7 @@ LAYOUT_NAMES = ["".join("rc"[x] for x in l) for l in LAYOUTS]
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # DRAM bytes (read + write) of one 8192^3 bf16->f32 launch of gemm_umma_kernel, from the ncu
 # capture summarised in profiles/gemm_umma_8192cubed_bf16_f32.md.
-NCU_DRAM_BYTES_PER_LAUNCH_8192 = 1.19e9
+NCU_DRAM_BYTES_PER_LAUNCH_8192 = 1.079e9  # 0.841 GB read + 0.237 GB written
 REPEATS_N1 = 16  # passes over the 8 layouts per step: 20 steps x 128 GEMMs x ~0.8 ms = 2 s
 
 

@@ -1004,67 +1004,73 @@ __global__ void __launch_bounds__(256)
 // Fix-up pass of the balanced (stream-K) schedule: out(tile) = convert(sum of the tile's partial
 // tiles), partials added in K order (ascending worker), so the result does not depend on timing.
 // `ws` holds one dense tile_m x tile_n f32 tile per slot; tile t's partials are the slots
-// t + w for the workers w whose runs overlap the tile's K steps (see WorkCursor).  One block
-// handles 32 rows of one tile per step; N is a multiple of 4, so a float4 never straddles the
-// matrix edge.  HBM/L2-bound: (parts x 4 + sizeof(out)) bytes per element.
+// t + w for the workers w whose runs overlap the tile's K steps (see WorkCursor).  N is a
+// multiple of 4, so a float4 never straddles the matrix edge.  HBM/L2-bound: (parts x 4 + sizeof(out)) bytes per element.
 // ---------------------------------------------------------------------------------------------
 template <int OUT>
 __global__ void __launch_bounds__(256)
     streamk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ out, const GemmParams p, uint32_t tile_m,
                           uint32_t tile_n)
 {
-    const uint32_t groups   = tile_m / 32u;
     const uint32_t tiles    = p.m_tiles * p.n_tiles;
-    const uint32_t jobs     = tiles * p.batch * groups;
     const uint32_t row4     = tile_n / 4u; // float4 per tile row
     const uint64_t tile_sz4 = static_cast<uint64_t>(tile_m) * row4;
+    const uint64_t total4   = tile_sz4 * tiles * p.batch;
     ptx::grid_dep_wait(); // the partials are complete once the GEMM grid before this one has finished
     ptx::grid_dep_launch();
-    for (uint32_t job = blockIdx.x; job < jobs; job += gridDim.x) {
-        const uint32_t tile = job / groups; // over batch x tiles
-        const uint32_t g    = job - tile * groups;
+    // One float4 of one tile per thread and step: thousands of independent loads in flight (a tile
+    // has only a handful of partials, so the sum itself is short).
+    for (uint64_t i = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x; i < total4;
+         i += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        const uint32_t tile = static_cast<uint32_t>(i / tile_sz4); // over batch x tiles
+        const uint32_t e    = static_cast<uint32_t>(i - tile * tile_sz4);
+        const uint32_t rr = e / row4, c4 = e - rr * row4;
+        uint32_t       m_idx, n_idx;
+        tile_coords(p, tile % tiles, m_idx, n_idx);
+        const uint32_t row = m_idx * tile_m + rr, col = n_idx * tile_n + c4 * 4u;
+        if (row >= p.M || col >= p.N) continue;
         // workers whose runs hold the tile's first and last K step
         const uint64_t x0 = static_cast<uint64_t>(tile) * p.units_per_tile, x1 = x0 + p.units_per_tile - 1u;
         const uint32_t w0 = static_cast<uint32_t>(((x0 + 1u) * p.workers + p.total_units - 1u) / p.total_units) - 1u;
         const uint32_t w1 = static_cast<uint32_t>(((x1 + 1u) * p.workers + p.total_units - 1u) / p.total_units) - 1u;
-        uint32_t       m_idx, n_idx;
-        tile_coords(p, tile % tiles, m_idx, n_idx);
+        const float4*  src = reinterpret_cast<const float4*>(ws) + static_cast<uint64_t>(tile + w0) * tile_sz4 + e;
+        float4         acc = __ldg(src);
+        uint32_t       w   = w0 + 1u;
+        for (; w + 3u <= w1; w += 4u) { // four loads in flight, added in K order
+            const float4 t0 = __ldg(src + tile_sz4), t1 = __ldg(src + 2u * tile_sz4), t2 = __ldg(src + 3u * tile_sz4),
+                         t3 = __ldg(src + 4u * tile_sz4);
+            src += 4u * tile_sz4;
+            acc.x = ((((acc.x + t0.x) + t1.x) + t2.x) + t3.x);
+            acc.y = ((((acc.y + t0.y) + t1.y) + t2.y) + t3.y);
+            acc.z = ((((acc.z + t0.z) + t1.z) + t2.z) + t3.z);
+            acc.w = ((((acc.w + t0.w) + t1.w) + t2.w) + t3.w);
+        }
+        for (; w <= w1; ++w) {
+            src += tile_sz4;
+            const float4 t = __ldg(src);
+            acc.x += t.x;
+            acc.y += t.y;
+            acc.z += t.z;
+            acc.w += t.w;
+        }
         const uint32_t z  = tile / tiles;
-        const uint32_t m0 = m_idx * tile_m + g * 32u, n0 = n_idx * tile_n;
-        if (m0 >= p.M) continue;
-        const float4* base = reinterpret_cast<const float4*>(ws) + static_cast<uint64_t>(g) * 32u * row4;
-        for (uint32_t idx = threadIdx.x; idx < 32u * row4; idx += blockDim.x) {
-            const uint32_t rr = idx / row4, c4 = idx - rr * row4;
-            const uint32_t row = m0 + rr, col = n0 + c4 * 4u;
-            if (row >= p.M || col >= p.N) continue;
-            const float4* src = base + static_cast<uint64_t>(tile + w0) * tile_sz4 + idx;
-            float4        acc = __ldg(src);
-            for (uint32_t w = w0 + 1u; w <= w1; ++w) {
-                src += tile_sz4;
-                const float4 t = __ldg(src);
-                acc.x += t.x;
-                acc.y += t.y;
-                acc.z += t.z;
-                acc.w += t.w;
-            }
-            const uint64_t at = (static_cast<uint64_t>(z) * p.M + row) * p.N + col; // element index; col % 4 == 0
-            if constexpr (OUT == OUT_F32) {
-                *reinterpret_cast<float4*>(static_cast<float*>(out) + at) = acc;
-            } else if constexpr (OUT == OUT_F16) {
-                const __half2 a = __floats2half2_rn(acc.x, acc.y);
-                const __half2 b = __floats2half2_rn(acc.z, acc.w);
-                uint2         u;
-                u.x = *reinterpret_cast<const uint32_t*>(&a);
-                u.y = *reinterpret_cast<const uint32_t*>(&b);
-                *reinterpret_cast<uint2*>(static_cast<__half*>(out) + at) = u;
-            } else {
-                const __nv_bfloat162 a = __floats2bfloat162_rn(acc.x, acc.y);
-                const __nv_bfloat162 b = __floats2bfloat162_rn(acc.z, acc.w);
-                uint2                u;
-                u.x = *reinterpret_cast<const uint32_t*>(&a);
-                u.y = *reinterpret_cast<const uint32_t*>(&b);
-                *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(out) + at) = u;
-            }
+        const uint64_t at = (static_cast<uint64_t>(z) * p.M + row) * p.N + col; // element index; col % 4 == 0
+        if constexpr (OUT == OUT_F32) {
+            *reinterpret_cast<float4*>(static_cast<float*>(out) + at) = acc;
+        } else if constexpr (OUT == OUT_F16) {
+            const __half2 a = __floats2half2_rn(acc.x, acc.y);
+            const __half2 b = __floats2half2_rn(acc.z, acc.w);
+            uint2         u;
+            u.x = *reinterpret_cast<const uint32_t*>(&a);
+            u.y = *reinterpret_cast<const uint32_t*>(&b);
+            *reinterpret_cast<uint2*>(static_cast<__half*>(out) + at) = u;
+        } else {
+            const __nv_bfloat162 a = __floats2bfloat162_rn(acc.x, acc.y);
+            const __nv_bfloat162 b = __floats2bfloat162_rn(acc.z, acc.w);
+            uint2                u;
+            u.x = *reinterpret_cast<const uint32_t*>(&a);
+            u.y = *reinterpret_cast<const uint32_t*>(&b);
+            *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(out) + at) = u;
         }
     }
 }

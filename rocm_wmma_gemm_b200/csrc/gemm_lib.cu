@@ -1064,7 +1064,11 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
         gp.stagger          = std::min<uint32_t>(want, kb_per_split / 2);
     }
     // Streaming (HBM-bound) views rotate the K order per work unit; see the producer.
-    const bool streaming = narrow || std::min(v.M, v.N) <= 256;
+    static const int k_skew_env = [] { // B200_GEMM_K_SKEW = 0 / 1 forces the rotation off / on (profiling)
+        const char* e = getenv("B200_GEMM_K_SKEW");
+        return (e && *e) ? atoi(e) : -1;
+    }();
+    const bool streaming = k_skew_env >= 0 ? k_skew_env != 0 : (narrow || std::min(v.M, v.N) <= 256);
     const uint32_t slots_per_unit = (kb_per_split + kc - 1) / kc; // K steps of one work unit
     gp.k_skew = streaming ? std::max<uint32_t>(1u, slots_per_unit / std::max<uint32_t>(1u, std::min<uint32_t>((uint32_t)work, (uint32_t)env.sm_count))) : 0u;
 
@@ -1178,8 +1182,8 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
     }
 
     if (balanced) {
-        const uint64_t jobs   = work * (tile_rows / 32u);
-        const unsigned blocks = (unsigned)std::min<uint64_t>(jobs, (uint64_t)env.sm_count * 8);
+        const uint64_t total4 = work * tile_rows * (uint64_t)(bn / 4);
+        const unsigned blocks = (unsigned)std::min<uint64_t>((total4 + 255) / 256, (uint64_t)env.sm_count * 8);
         e = launch_streamk_reduce(out, blocks, stream, ws, v.d, gp, tile_rows, (uint32_t)bn);
         g_launches.fetch_add(1, std::memory_order_relaxed);
         if (ws_stream_ordered) cudaFreeAsync(ws, stream);

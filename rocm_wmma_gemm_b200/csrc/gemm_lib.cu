@@ -889,7 +889,16 @@ static int make_plan(const Problem& p, const b200_gemm_config* user_cfg, int sm_
         auto slots_fit = [&](uint32_t c) {
             return transposed ? slab_max_stages((int)bm, cfg.tile_n, (int)c) : slot_max_stages(cfg.tile_n, (int)c);
         };
-        while (kc > 1 && (kb_per_split < 2 * kc || slots_fit(kc) < 3)) kc /= 2;
+        uint32_t min_slots = 3;
+        static const int kc_env = [] { // B200_GEMM_KC = 1 / 2 / 4 forces the k-blocks per ring slot where two slots fit (profiling)
+            const char* e = getenv("B200_GEMM_KC");
+            return (e && *e) ? atoi(e) : 0;
+        }();
+        if (kc_env == 1 || kc_env == 2 || kc_env == 4) {
+            kc        = (uint32_t)kc_env;
+            min_slots = 2;
+        }
+        while (kc > 1 && (kb_per_split < 2 * kc || slots_fit(kc) < (int)min_slots)) kc /= 2;
         if (cfg.split_k > 1 && kb_per_split % kc) { // partitions start on slot boundaries
             const uint32_t k_blocks = (v.K + BLOCK_K - 1) / BLOCK_K;
             kb_per_split            = (kb_per_split + kc - 1) / kc * kc;

@@ -393,7 +393,10 @@ def run_b200(args, rank, world, local_rank):
                                             "vendor_burst = best of 4 after 0.25 s idle"}
         del o2, o2f
     if world > 1 and wl["kind"] == "slab":
-        extra.update(multi_gpu_extras(args, g, L, dist, dev, rank, world, wl, A, B, C, n_local, slab_of_b, barrier, value))
+        try:
+            extra.update(multi_gpu_extras(args, g, L, dist, dev, rank, world, wl, A, B, C, n_local, slab_of_b, barrier, value))
+        except Exception as ex:  # the compute-only line must survive a failure of what is reported beside it
+            extra["multi_gpu_extras_error"] = f"{type(ex).__name__}: {ex}"[:400]
 
     # ---- end to end through the host-buffer entry points -----------------------------------------
     e2e_steps = max(1, min(args.steps, 3))

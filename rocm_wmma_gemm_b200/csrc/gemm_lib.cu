@@ -1063,6 +1063,7 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
     gp.out    = nullptr;
     gp.ndst = 0;
     gp.dst_row0 = gp.dst_col0 = 0;
+
     gp.l2_hints = env_l2_hints() >= 0 ? (uint32_t)env_l2_hints() : default_l2_hints(v, gp, p.batch, out_is_f32(p.types) ? 4 : 2);
     // 512-wide tiles stagger their two column halves so the epilogue of one half hides under the
     // MMAs of the other (TileStep in gemm_kernels.cuh).  The stagger covers the time one half
@@ -1482,8 +1483,23 @@ extern "C" int b200_gemm_host(int types, void* C, const void* A, const void* B, 
             b.push_back(dim);
             return b;
         }
-        const size_t step = ((dim + 3) / 4 + 255) / 256 * 256;
-        size_t       at   = 0;
+        // B200_GEMM_HOST_CHUNKS="first,count" (profiling): a first chunk of `first` rows / columns,
+        // the rest in `count` equal chunks.  Default: the measured optimum below.
+        static const struct Scheme {
+            size_t first = 0, count = 4;
+            Scheme()
+            {
+                const char* e = getenv("B200_GEMM_HOST_CHUNKS");
+                unsigned long f = 0, c = 0;
+                if (e && sscanf(e, "%lu,%lu", &f, &c) == 2 && c >= 1 && c <= 12) {
+                    first = f / 256 * 256;
+                    count = c;
+                }
+            }
+        } scheme;
+        size_t at = 0;
+        if (scheme.first && scheme.first < dim / 2) b.push_back(at = scheme.first);
+        const size_t step = ((dim - at + scheme.count - 1) / scheme.count + 255) / 256 * 256;
         while (dim - at > step) b.push_back(at += step);
         b.push_back(dim);
         return b;

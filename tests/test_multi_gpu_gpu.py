@@ -151,3 +151,20 @@ def test_three_gathers_match_the_reference_on_every_rank(tmp_path, world):
     for r in range(world):
         text = open(tmp_path / f"rank{r}.txt").read()
         assert text == "", text
+
+
+def test_slab_driver_from_plain_cpp():
+    """tests/cpp/test_slab_driver.cpp: host threads as ranks, plain peer pointers, no Python in
+    the loop - the fused gather and the NCCL all-gather against the CPU reference on every rank."""
+    import shutil
+    import subprocess
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    if shutil.which("g++") is None or shutil.which("gcc") is None:
+        pytest.skip("no host C++ compiler on this machine")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    built = subprocess.run(["sh", os.path.join(root, "tests", "cpp", "build_slab_test.sh")], capture_output=True, text=True, timeout=600)
+    assert built.returncode == 0, built.stdout + built.stderr
+    proc = subprocess.run([os.path.join(root, "tests", "cpp", "test_slab_driver")], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert "0 failed" in proc.stdout

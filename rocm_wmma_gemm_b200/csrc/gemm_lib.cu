@@ -923,8 +923,9 @@ struct LaunchEnv {
     size_t        fixed_ws_bytes; // ... and its size
 };
 
-// L2 eviction priorities of the TMA traffic (GemmParams::l2_hints).  B200_GEMM_L2_HINTS, read
-// once, overrides the launch path's own choice (profiling).
+// L2 eviction priorities of the TMA traffic (GemmParams::l2_hints); only builds with
+// -DB200_GEMM_L2_HINT_BUILD act on them.  B200_GEMM_L2_HINTS, read once, overrides the launch
+// path's own choice (profiling).
 static int env_l2_hints()
 {
     static const int v = [] {

@@ -36,7 +36,7 @@ CASES = [
     (3, 384, 1536, 192, 1, 1, 0, 256),   # f32 out, column-major C: slabs concatenate
     (0, 256, 1280, 128, 0, 0, 0, 256),   # f16, ragged slabs at 2 and 4 ranks (N is not a multiple of world x align)
     (1, 520, 2048, 320, 0, 1, 1, 64),    # f32 out, ragged M (edge tiles clipped inside the full matrix)
-    (2, 2304, 1024, 128, 0, 0, 1, 256),  # tall enough for the host-buffer call's row panels
+    (2, 4608, 1024, 128, 0, 0, 1, 256),  # tall enough for the host-buffer call to work in two row panels
 ]
 
 

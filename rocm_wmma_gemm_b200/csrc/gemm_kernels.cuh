@@ -466,24 +466,28 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
     const uint32_t ring = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u; // ring of operand tiles
     const uint32_t epi  = ring + stages * pitch;                      // epilogue staging (unused when TR)
 
-    if (tid == 0) {
-        ptx::prefetch_tensormap(&tmA);
-        ptx::prefetch_tensormap(&tmB);
-        if constexpr (GATHER) {
-            for (uint32_t d = 0; d < p.ndst; ++d) ptx::prefetch_tensormap(&tmDs[d]);
-        } else {
-            ptx::prefetch_tensormap(&tmD);
+    if (warp == 0) {
+        // Barrier set-up spread over the lanes of warp 0 (one thread doing all of it serially is
+        // a third of a microsecond of every launch; small problems notice).
+        if (lane == 0) {
+            ptx::prefetch_tensormap(&tmA);
+            ptx::prefetch_tensormap(&tmB);
+            if constexpr (GATHER) {
+                for (uint32_t d = 0; d < p.ndst; ++d) ptx::prefetch_tensormap(&tmDs[d]);
+            } else {
+                ptx::prefetch_tensormap(&tmD);
+            }
+            ptx::mbar_init(ptx::smem_u32(&s_drain), 1);
+            s_abort = 0u;
         }
-        for (uint32_t s = 0; s < stages; ++s) {
-            ptx::mbar_init(ptx::smem_u32(&s_full[s]), 1);
-            ptx::mbar_init(ptx::smem_u32(&s_empty[s]), 1);
+        if (lane < stages) {
+            ptx::mbar_init(ptx::smem_u32(&s_full[lane]), 1);
+            ptx::mbar_init(ptx::smem_u32(&s_empty[lane]), 1);
         }
-        for (int b = 0; b < 2; ++b) {
-            ptx::mbar_init(ptx::smem_u32(&s_tfull[b]), 1);
-            ptx::mbar_init(ptx::smem_u32(&s_tempty[b]), 4 * CL);
+        if (lane >= 30u) {
+            ptx::mbar_init(ptx::smem_u32(&s_tfull[lane - 30u]), 1);
+            ptx::mbar_init(ptx::smem_u32(&s_tempty[lane - 30u]), 4 * CL);
         }
-        ptx::mbar_init(ptx::smem_u32(&s_drain), 1);
-        s_abort = 0u;
         ptx::fence_mbar_init();
     }
     if (warp == 1) {
@@ -915,7 +919,9 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
             }
             } // halves
         }
-        if (lane == 0) ptx::tma_store_wait_all<0>();
+        // The staging buffers may go away once the stores have READ them; the writes themselves
+        // are complete when the grid is (and a dependent grid waits for exactly that).
+        if (lane == 0) ptx::tma_store_wait_read<0>();
     }
 
     // ---------------------------------------------------------------------- tail

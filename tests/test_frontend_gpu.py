@@ -33,13 +33,16 @@ def test_cpp_front_end(gemm_lib):
     assert m and int(m.group(1)) == 4 * 8 * 5 * 2 + 3 + 2 and int(m.group(2)) == 0, proc.stdout[-2000:]
 
 
-def test_reference_typed_test_compiled_against_this_front_end():
-    """The reference's own test/gemm/test_float_accum.cpp, compiled unmodified against include/
-    (tests/cpp/build_reference_test.sh, run where a reference checkout exists; the binary
-    travels with the tree) with a minimal stand-in for the test framework it includes."""
-    binary = os.path.join(CPP, "test_reference_float_accum")
+@pytest.mark.parametrize("name", ["float_accum", "same_prec"])
+def test_reference_typed_tests_compiled_against_this_front_end(name):
+    """The reference's own test/gemm/test_float_accum.cpp (f32 outputs, 1e-4 per element) and
+    test/gemm/test_same_prec.cpp (f16 / bf16 outputs, cosine similarity), compiled unmodified
+    against include/ (tests/cpp/build_reference_test.sh, run where a reference checkout exists;
+    the binaries travel with the tree) with a minimal stand-in for the test framework they
+    include: 16 type x layout instantiations x 13 sizes each."""
+    binary = os.path.join(CPP, f"test_reference_{name}")
     if not os.path.exists(binary):
-        pytest.skip("tests/cpp/test_reference_float_accum has not been built (needs a reference checkout)")
+        pytest.skip(f"tests/cpp/test_reference_{name} has not been built (needs a reference checkout)")
     proc = _run(binary)
     assert proc.returncode == 0, proc.stdout[-4000:] + proc.stderr[-2000:]
     m = re.search(r"(\d+) tests ran, (\d+) failed", proc.stdout)

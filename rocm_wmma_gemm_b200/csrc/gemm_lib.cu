@@ -923,9 +923,9 @@ struct LaunchEnv {
     size_t        fixed_ws_bytes; // ... and its size
 };
 
-// L2 eviction priorities of the TMA traffic (GemmParams::l2_hints); only builds with
-// -DB200_GEMM_L2_HINT_BUILD act on them.  B200_GEMM_L2_HINTS, read once, overrides the launch
-// path's own choice (profiling).
+// L2 eviction priorities of the TMA traffic (GemmParams::l2_hints, 0 = none); only builds with
+// -DB200_GEMM_L2_HINT_BUILD act on them.  B200_GEMM_L2_HINTS, read once, sets them (profiling);
+// no policy measured better than none, so the launch path itself never asks for one.
 static int env_l2_hints()
 {
     static const int v = [] {
@@ -933,13 +933,6 @@ static int env_l2_hints()
         return (e && *e) ? atoi(e) : -1;
     }();
     return v;
-}
-
-// The launch path's own choice of L2 eviction priorities for the TMA traffic of one problem.
-static uint32_t default_l2_hints(const View& v, const GemmParams& gp, size_t batch, size_t out_sz)
-{
-    (void)v; (void)gp; (void)batch; (void)out_sz;
-    return 0u;
 }
 
 // A GEMM whose output is a block of a larger matrix held once per GPU: every tile is stored to
@@ -1065,7 +1058,7 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
     gp.ndst = 0;
     gp.dst_row0 = gp.dst_col0 = 0;
 
-    gp.l2_hints = env_l2_hints() >= 0 ? (uint32_t)env_l2_hints() : default_l2_hints(v, gp, p.batch, out_is_f32(p.types) ? 4 : 2);
+    gp.l2_hints = env_l2_hints() >= 0 ? (uint32_t)env_l2_hints() : 0u;
     // 512-wide tiles stagger their two column halves so the epilogue of one half hides under the
     // MMAs of the other (TileStep in gemm_kernels.cuh).  The stagger covers the time one half
     // takes to drain: about 5.5k cycles for f32 output, 3.3k for 16-bit, at 512 cycles per k-block.

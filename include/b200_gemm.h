@@ -103,8 +103,9 @@ enum b200_gemm_types {
  *   split_k  number of K partitions reduced through an f32 workspace (1 = none).  0 selects the
  *            balanced schedule (stream-K, the reference's roadmap item README.md:202): the K
  *            loops of all tiles are laid end to end and cut into one equal run per SM, so every
- *            SM does the same number of K steps whatever the tile count; partial tiles meet in
- *            a deterministic fix-up pass.  Needs tile_n <= 256 and N % 4 == 0 in the kernel view.
+ *            SM does the same number of K steps whatever the tile count; tiles a run covers
+ *            whole go straight to C, the tiles a run boundary cuts meet as f32 partials in a
+ *            deterministic fix-up pass.  Needs tile_n <= 256 and N % 4 == 0 in the kernel view.
  *   raster   tile-rows per raster band (the reference's `swizzle` key,
  *            rocm_wmma_gemm/include/rocm_wmma_gemm/kernel/mapping.hpp:108-287); 0 = column sweep.
  *            Adding B200_GEMM_RASTER_SNAKE selects the boustrophedon order of the reference's

@@ -185,6 +185,7 @@ struct WorkCoord {
     uint32_t z_in;     // batch index (third TMA coordinate of A' and B')
     uint32_t z_out;    // third TMA coordinate of D: batch * split_k + split
     uint32_t kb0, kb1; // k-block range
+    uint32_t partial;  // balanced schedule: the segment is only part of its tile's K loop (f32 partial to the workspace)
 };
 
 // Tile index -> (tile-row, tile-column) under the problem's raster.
@@ -231,6 +232,7 @@ __device__ __forceinline__ WorkCoord decode_work(const GemmParams& p, uint32_t w
     c.z_out = b * p.split_k + split;
     c.kb0   = split * p.kb_per_split;
     c.kb1   = min(p.k_blocks, c.kb0 + p.kb_per_split);
+    c.partial = 0u;
     return c;
 }
 
@@ -244,11 +246,12 @@ __device__ __forceinline__ WorkCoord decode_work(const GemmParams& p, uint32_t w
 // K loops are laid end to end - tile 0's K steps, then tile 1's, ... - and that line of
 // total_units steps is cut into `workers` equal runs, one per worker, wherever the cuts fall.
 // A worker walks its run segment by segment (a segment = the part of one tile's K loop inside
-// the run), so every SM gets the same number of K steps whatever the tile count.  Every segment
-// leaves an f32 partial tile in the workspace at slot (tile + worker) - along the line either
-// the tile or the worker advances from one segment to the next, so the sum is unique - and the
-// fix-up pass (streamk_reduce_kernel) adds a tile's partials in K order.  No CTA waits for
-// another.
+// the run), so every SM gets the same number of K steps whatever the tile count.  A segment
+// that covers a tile's whole K loop stores the tile to C like the plain schedule does.  A
+// partial segment leaves an f32 partial tile in the workspace: a run has at most two of them,
+// its first (it starts inside a tile: slot 2 * worker) and its last (it ends inside a tile:
+// slot 2 * worker + 1); the fix-up pass (streamk_reduce_kernel) adds a split tile's partials in
+// K order and writes C.  No CTA waits for another.
 // ---------------------------------------------------------------------------------------------
 struct WorkCursor {
     uint32_t next;  // plain: next work item; balanced: next K step of the run
@@ -291,10 +294,12 @@ __device__ __forceinline__ bool work_next(const GemmParams& p, WorkCursor& cur, 
     tile_coords(p, tile % tiles, m_idx, n_idx);
     c.m0    = m_idx * static_cast<uint32_t>(bm);
     c.n0    = n_idx * static_cast<uint32_t>(bn);
-    c.z_in  = tile / tiles;
-    c.z_out = tile + unit; // workspace slot of this segment's partial tile
-    c.kb0   = first * p.kc;
-    c.kb1   = min(p.k_blocks, last * p.kc);
+    c.z_in    = tile / tiles;
+    c.partial = (first != 0u || last != p.units_per_tile) ? 1u : 0u;
+    // whole tile: third coordinate of C (the batch index); partial: the workspace slot
+    c.z_out   = c.partial ? 2u * unit + (first != 0u ? 0u : 1u) : c.z_in;
+    c.kb0     = first * p.kc;
+    c.kb1     = min(p.k_blocks, last * p.kc);
     cur.next += last - first;
     return true;
 }
@@ -398,7 +403,7 @@ __device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits)
 // ---------------------------------------------------------------------------------------------
 template <int BN, int OUT, int CL, bool TR, bool GATHER>
 __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUtensorMap& tmB,
-                                               const CUtensorMap* tmDs, const GemmParams& p)
+                                               const CUtensorMap* tmDs, const CUtensorMap& tmW, const GemmParams& p)
 {
     const CUtensorMap& tmD = tmDs[0];
     static_assert(BN == 16 || BN == 32 || BN == 64 || BN == 128 || BN == 256 || BN == 512,
@@ -852,29 +857,34 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                 continue;
             }
             // Software pipeline over 128-byte column chunks: the TMEM load of chunk ch + 1 is
-            // in flight while chunk ch is converted, staged and handed to the TMA store.
+            // in flight while chunk ch is converted, staged and handed to the TMA store.  `O` is
+            // the element kind written: the kernel's output type, or f32 for a partial tile of
+            // the balanced schedule (tile-local coordinates in the workspace map `tm`).
+            auto drain = [&](auto out_tag, const CUtensorMap* tm, bool tile_local) {
+            constexpr int O    = decltype(out_tag)::value;
+            constexpr int O_CH = (O == OUT_F32) ? 32 : 64; // output columns per 128-byte chunk
             uint32_t       n0[32], n1[32]; // raw accumulator words of the chunk in flight
             ptx::tmem_ld_32x32(tacc, n0);
-            if constexpr (OUT != OUT_F32) ptx::tmem_ld_32x32(tacc + 32u, n1);
-            const int NCH_H = FLEX ? static_cast<int>(wn) / CH : NCHUNK / NSUB; // chunks per half
+            if constexpr (O != OUT_F32) ptx::tmem_ld_32x32(tacc + 32u, n1);
+            const int NCH_H = FLEX ? static_cast<int>(wn) / O_CH : (BN < O_CH ? 1 : BN / O_CH) / NSUB; // chunks per half
 #pragma unroll 1
             for (int ch = 0; ch < NCH_H; ++ch) {
                 uint32_t v[32];
                 ptx::tmem_ld_wait(n0);
-                if constexpr (OUT == OUT_F32) {
+                if constexpr (O == OUT_F32) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = n0[j];
                 } else {
                     ptx::tmem_ld_wait(n1);
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        v[j]      = pack2<OUT>(n0[2 * j], n0[2 * j + 1]);
-                        v[16 + j] = pack2<OUT>(n1[2 * j], n1[2 * j + 1]);
+                        v[j]      = pack2<O>(n0[2 * j], n0[2 * j + 1]);
+                        v[16 + j] = pack2<O>(n1[2 * j], n1[2 * j + 1]);
                     }
                 }
                 if (ch + 1 < NCH_H) {
-                    ptx::tmem_ld_32x32(tacc + (ch + 1) * CH, n0);
-                    if constexpr (OUT != OUT_F32) ptx::tmem_ld_32x32(tacc + (ch + 1) * CH + 32u, n1);
+                    ptx::tmem_ld_32x32(tacc + (ch + 1) * O_CH, n0);
+                    if constexpr (O != OUT_F32) ptx::tmem_ld_32x32(tacc + (ch + 1) * O_CH + 32u, n1);
                 }
                 if (ch == NCH_H - 1) {
                     // Accumulator (half) fully read: hand it back to the MMA issuer (rank 0).
@@ -885,7 +895,7 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                         else ptx::mbar_arrive(ptx::smem_u32(&s_tempty[bar_i]));
                     }
                 }
-                const uint32_t col0 = c.n0 + colh + ch * CH;
+                const uint32_t col0 = c.n0 + colh + ch * O_CH;
                 if (row_live && col0 < p.N) {
                     const uint32_t sbuf = stg + (nstore & 1u) * EPI_BUF_BYTES;
                     // The store that last used this buffer (two stores ago) must have read it.
@@ -906,16 +916,23 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                             // output happens tile by tile under the main loop of the next tile.
                             for (uint32_t d = 0; d < p.ndst; ++d)
                                 ptx::tma_store_3d(&tmDs[d], sbuf, col0 + p.dst_col0, row0 + p.dst_row0, c.z_out, pol_d);
-                        } else if (p.balanced) {
-                            // partial tile: tile-local coordinates, one workspace slot per segment
-                            ptx::tma_store_3d(&tmD, sbuf, col0 - c.n0, row0 - c.m0, c.z_out, pol_d);
+                        } else if (tile_local) {
+                            ptx::tma_store_3d(tm, sbuf, col0 - c.n0, row0 - c.m0, c.z_out, pol_d);
                         } else {
-                            ptx::tma_store_3d(&tmD, sbuf, col0, row0, c.z_out, pol_d);
+                            ptx::tma_store_3d(tm, sbuf, col0, row0, c.z_out, pol_d);
                         }
                         ptx::tma_store_commit();
                     }
                     ++nstore;
                 }
+            }
+            }; // drain
+            if constexpr (!GATHER && NSUB == 1 && !TR) {
+                // balanced schedule: partial segments go to the workspace as f32, whole tiles to C
+                if (c.partial) drain(std::integral_constant<int, OUT_F32>{}, &tmW, true);
+                else drain(std::integral_constant<int, OUT>{}, &tmD, false);
+            } else {
+                drain(std::integral_constant<int, OUT>{}, &tmD, false);
             }
             } // halves
         }
@@ -942,9 +959,11 @@ template <int BN, int OUT, int CL, bool TR = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
     gemm_umma_kernel(const __grid_constant__ CUtensorMap tmA,
                      const __grid_constant__ CUtensorMap tmB,
-                     const __grid_constant__ CUtensorMap tmD, const GemmParams p)
+                     const __grid_constant__ CUtensorMap tmD,
+                     const __grid_constant__ CUtensorMap tmW, const GemmParams p)
 {
-    gemm_umma_body<BN, OUT, CL, TR, false>(tmA, tmB, &tmD, p);
+    // tmW: the balanced schedule's workspace of f32 partial tiles (any valid map otherwise)
+    gemm_umma_body<BN, OUT, CL, TR, false>(tmA, tmB, &tmD, tmW, p);
 }
 
 // The same GEMM with the all-gather of its output fused into the epilogue: this GPU computes a
@@ -957,7 +976,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                             const __grid_constant__ CUtensorMap tmB,
                             const __grid_constant__ GatherMaps dst, const GemmParams p)
 {
-    gemm_umma_body<BN, OUT, CL, false, true>(tmA, tmB, dst.m, p);
+    gemm_umma_body<BN, OUT, CL, false, true>(tmA, tmB, dst.m, dst.m[0], p);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1007,59 +1026,59 @@ __global__ void __launch_bounds__(256)
 }
 
 // ---------------------------------------------------------------------------------------------
-// Fix-up pass of the balanced (stream-K) schedule: out(tile) = convert(sum of the tile's partial
-// tiles), partials added in K order (ascending worker), so the result does not depend on timing.
-// `ws` holds one dense tile_m x tile_n f32 tile per slot; tile t's partials are the slots
-// t + w for the workers w whose runs overlap the tile's K steps (see WorkCursor).  N is a
-// multiple of 4, so a float4 never straddles the matrix edge.  HBM/L2-bound: (parts x 4 + sizeof(out)) bytes per element.
+// Fix-up pass of the balanced (stream-K) schedule: for every tile that a run boundary cuts,
+// out(tile) = convert(sum of the tile's partial tiles), partials added in K order (ascending
+// worker), so the result does not depend on timing.  Tiles no boundary cuts were written to C
+// by the GEMM kernel itself and are not touched.
+//
+// Job j (1 <= j < workers) belongs to the boundary between runs j - 1 and j.  The boundary cuts
+// a tile unless it falls on a tile's first K step; a tile cut by several boundaries is handled
+// by the job of the first of them.  The tile's contributors are the workers w0 .. w1 whose runs
+// hold its first and last K step; worker w's partial sits in slot 2w if its run starts inside
+// the tile, in slot 2w + 1 if its run came in through the tile's first K step (see WorkCursor).
+// `ws` holds one dense tile_m x tile_n f32 tile per slot.  N is a multiple of 4, so a float4
+// never straddles the matrix edge.  L2/HBM-bound: (parts x 4 + sizeof(out)) bytes per element
+// of a cut tile; blockIdx.y = job, blockIdx.x strides over the tile's float4s.
 // ---------------------------------------------------------------------------------------------
 template <int OUT>
 __global__ void __launch_bounds__(256)
     streamk_reduce_kernel(const float* __restrict__ ws, void* __restrict__ out, const GemmParams p, uint32_t tile_m,
                           uint32_t tile_n)
 {
-    const uint32_t tiles    = p.m_tiles * p.n_tiles;
-    const uint32_t row4     = tile_n / 4u; // float4 per tile row
-    const uint64_t tile_sz4 = static_cast<uint64_t>(tile_m) * row4;
-    const uint64_t total4   = tile_sz4 * tiles * p.batch;
     ptx::grid_dep_wait(); // the partials are complete once the GEMM grid before this one has finished
     ptx::grid_dep_launch();
-    // One float4 of one tile per thread and step: thousands of independent loads in flight (a tile
-    // has only a handful of partials, so the sum itself is short).
-    for (uint64_t i = blockIdx.x * static_cast<uint64_t>(blockDim.x) + threadIdx.x; i < total4;
-         i += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
-        const uint32_t tile = static_cast<uint32_t>(i / tile_sz4); // over batch x tiles
-        const uint32_t e    = static_cast<uint32_t>(i - tile * tile_sz4);
+    const uint32_t j        = blockIdx.y + 1u;
+    const uint32_t upt      = p.units_per_tile;
+    const uint32_t boundary = run_start(p, j);
+    const uint32_t tile     = boundary / upt; // over batch x tiles
+    const uint32_t tile_beg = tile * upt;
+    if (boundary == tile_beg) return;                             // the cut falls between two tiles
+    if (j > 1u && run_start(p, j - 1u) > tile_beg) return;        // an earlier boundary owns this tile
+    // workers whose runs hold the tile's first and last K step
+    const uint64_t x0 = tile_beg, x1 = x0 + upt - 1u;
+    const uint32_t w0 = static_cast<uint32_t>(((x0 + 1u) * p.workers + p.total_units - 1u) / p.total_units) - 1u;
+    const uint32_t w1 = static_cast<uint32_t>(((x1 + 1u) * p.workers + p.total_units - 1u) / p.total_units) - 1u;
+    const uint32_t tiles    = p.m_tiles * p.n_tiles;
+    const uint32_t row4     = tile_n / 4u; // float4 per tile row
+    const uint32_t tile_sz4 = tile_m * row4;
+    uint32_t       m_idx, n_idx;
+    tile_coords(p, tile % tiles, m_idx, n_idx);
+    const uint32_t z    = tile / tiles;
+    const float4*  ws4  = reinterpret_cast<const float4*>(ws);
+    // the first contributor's run holds the tile's first K step: its partial is its run's last segment
+    const uint32_t slot0 = 2u * w0 + 1u;
+    for (uint32_t e = blockIdx.x * blockDim.x + threadIdx.x; e < tile_sz4; e += gridDim.x * blockDim.x) {
         const uint32_t rr = e / row4, c4 = e - rr * row4;
-        uint32_t       m_idx, n_idx;
-        tile_coords(p, tile % tiles, m_idx, n_idx);
         const uint32_t row = m_idx * tile_m + rr, col = n_idx * tile_n + c4 * 4u;
         if (row >= p.M || col >= p.N) continue;
-        // workers whose runs hold the tile's first and last K step
-        const uint64_t x0 = static_cast<uint64_t>(tile) * p.units_per_tile, x1 = x0 + p.units_per_tile - 1u;
-        const uint32_t w0 = static_cast<uint32_t>(((x0 + 1u) * p.workers + p.total_units - 1u) / p.total_units) - 1u;
-        const uint32_t w1 = static_cast<uint32_t>(((x1 + 1u) * p.workers + p.total_units - 1u) / p.total_units) - 1u;
-        const float4*  src = reinterpret_cast<const float4*>(ws) + static_cast<uint64_t>(tile + w0) * tile_sz4 + e;
-        float4         acc = __ldg(src);
-        uint32_t       w   = w0 + 1u;
-        for (; w + 3u <= w1; w += 4u) { // four loads in flight, added in K order
-            const float4 t0 = __ldg(src + tile_sz4), t1 = __ldg(src + 2u * tile_sz4), t2 = __ldg(src + 3u * tile_sz4),
-                         t3 = __ldg(src + 4u * tile_sz4);
-            src += 4u * tile_sz4;
-            acc.x = ((((acc.x + t0.x) + t1.x) + t2.x) + t3.x);
-            acc.y = ((((acc.y + t0.y) + t1.y) + t2.y) + t3.y);
-            acc.z = ((((acc.z + t0.z) + t1.z) + t2.z) + t3.z);
-            acc.w = ((((acc.w + t0.w) + t1.w) + t2.w) + t3.w);
-        }
-        for (; w <= w1; ++w) {
-            src += tile_sz4;
-            const float4 t = __ldg(src);
+        float4 acc = __ldg(ws4 + static_cast<uint64_t>(slot0) * tile_sz4 + e);
+        for (uint32_t w = w0 + 1u; w <= w1; ++w) { // these runs start inside the tile: slot 2w
+            const float4 t = __ldg(ws4 + static_cast<uint64_t>(2u * w) * tile_sz4 + e);
             acc.x += t.x;
             acc.y += t.y;
             acc.z += t.z;
             acc.w += t.w;
         }
-        const uint32_t z  = tile / tiles;
         const uint64_t at = (static_cast<uint64_t>(z) * p.M + row) * p.N + col; // element index; col % 4 == 0
         if constexpr (OUT == OUT_F32) {
             *reinterpret_cast<float4*>(static_cast<float*>(out) + at) = acc;

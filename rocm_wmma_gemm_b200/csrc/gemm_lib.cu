@@ -638,7 +638,7 @@ static int encode_operand_slab(CUtensorMap* tm, bool bf16, const void* base, uin
 // ------------------------------------------------------------------------------------------
 template <int BN, int CL, bool TR = false>
 static cudaError_t launch_bn(int out, uint32_t units_wanted, PairCache* pairs, int pair_slot, uint32_t smem, cudaStream_t s,
-                             const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& d,
+                             const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& d, const CUtensorMap& w,
                              const GemmParams& gp, const GatherMaps* gather = nullptr)
 {
     cudaLaunchConfig_t lc = {};
@@ -693,9 +693,9 @@ static cudaError_t launch_bn(int out, uint32_t units_wanted, PairCache* pairs, i
         }
     }
     switch (out) {
-        case OUT_F32: return cudaLaunchKernelEx(&lc, gemm_umma_kernel<BN, OUT_F32, CL, TR>, a, b, d, gp);
-        case OUT_F16: return cudaLaunchKernelEx(&lc, gemm_umma_kernel<BN, OUT_F16, CL, TR>, a, b, d, gp);
-        default: return cudaLaunchKernelEx(&lc, gemm_umma_kernel<BN, OUT_BF16, CL, TR>, a, b, d, gp);
+        case OUT_F32: return cudaLaunchKernelEx(&lc, gemm_umma_kernel<BN, OUT_F32, CL, TR>, a, b, d, w, gp);
+        case OUT_F16: return cudaLaunchKernelEx(&lc, gemm_umma_kernel<BN, OUT_F16, CL, TR>, a, b, d, w, gp);
+        default: return cudaLaunchKernelEx(&lc, gemm_umma_kernel<BN, OUT_BF16, CL, TR>, a, b, d, w, gp);
     }
 }
 
@@ -744,11 +744,11 @@ static cudaError_t launch_reduce(int out, unsigned blocks, cudaStream_t s, const
 
 // Fix-up pass of the balanced schedule, a programmatic dependent of the GEMM kernel like the
 // split-K reduction.
-static cudaError_t launch_streamk_reduce(int out, unsigned blocks, cudaStream_t s, const float* ws, void* d, const GemmParams& gp,
-                                         uint32_t tile_m, uint32_t tile_n)
+static cudaError_t launch_streamk_reduce(int out, unsigned blocks, unsigned jobs, cudaStream_t s, const float* ws, void* d,
+                                         const GemmParams& gp, uint32_t tile_m, uint32_t tile_n)
 {
     cudaLaunchConfig_t lc = {};
-    lc.gridDim            = dim3(blocks);
+    lc.gridDim            = dim3(blocks, jobs);
     lc.blockDim           = dim3(256);
     lc.dynamicSmemBytes   = 0;
     lc.stream             = s;
@@ -1078,8 +1078,8 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
 
     // Split-K partials go to this stream's cached f32 workspace, laid out [batch][split][Mk][Nk].
     float*       ws       = nullptr;
-    // (balanced: one tile_rows x bn partial tile per segment, slots tile + worker)
-    const size_t ws_slots = balanced ? (size_t)work + gp.workers : 0;
+    // (balanced: one tile_rows x bn partial tile per partial segment, two slots per worker)
+    const size_t ws_slots = balanced ? 2 * (size_t)gp.workers : 0;
     const size_t ws_bytes = balanced ? ws_slots * tile_rows * bn * sizeof(float)
                                      : (split > 1 ? (size_t)p.batch * split * v.M * v.N * sizeof(float) : 0);
     bool         ws_stream_ordered = false;
@@ -1107,7 +1107,7 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
         }
     }
 
-    CUtensorMap tmA, tmB, tmD;
+    CUtensorMap tmA, tmB, tmD, tmW;
     if (slot) {
         st = encode_operand_slab(&tmA, bf16, v.a, v.M, v.K, p.batch, v.a_mn, bm, kc, k4d);
         if (st == B200_GEMM_OK) st = encode_operand_slab(&tmB, bf16, v.b, v.N, v.K, p.batch, v.b_mn, (uint32_t)bn, kc, k4d);
@@ -1115,19 +1115,21 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
         st = encode_operand(&tmA, bf16, v.a, v.M, v.K, p.batch, v.a_mn, BLOCK_M);
         if (st == B200_GEMM_OK) st = encode_operand(&tmB, bf16, v.b, v.N, v.K, p.batch, v.b_mn, (uint32_t)umma_n / cl);
     }
+    tmW = tmA; // only the balanced schedule uses it; any valid descriptor will do otherwise
     if (st == B200_GEMM_OK && transposed) {
         tmD    = tmA; // not used by the transposed epilogue; any valid descriptor will do
         gp.out = split > 1 ? static_cast<void*>(ws) : v.d;
     } else if (st == B200_GEMM_OK) {
-        if (balanced)
-            st = encode_map(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ws, (uint64_t)bn, tile_rows, ws_slots, 32, 32);
-        else if (split > 1)
+        if (split > 1)
             st = encode_map(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ws, v.N, v.M, (uint64_t)p.batch * split, 32, 32);
         else if (out == OUT_F32)
             st = encode_map(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, v.d, v.N, v.M, p.batch, 32, 32);
         else
             st = encode_map(&tmD, out == OUT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                             v.d, v.N, v.M, p.batch, 64, 32);
+        // balanced schedule: partial tiles in tile-local coordinates, one slot per partial segment
+        if (st == B200_GEMM_OK && balanced)
+            st = encode_map(&tmW, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ws, (uint64_t)bn, tile_rows, ws_slots, 32, 32);
     }
     GatherMaps gmaps;
     if (st == B200_GEMM_OK && gather) {
@@ -1156,26 +1158,26 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
     const uint32_t smem     = transposed ? slab_smem_bytes((int)bm, bn, (int)kc, cfg.stages)
                               : (slot ? slot_smem_bytes(bn, (int)kc, cfg.stages) : gemm_smem_bytes(compiled_width(bn), (int)cl, cfg.stages));
     const uint32_t units    = balanced ? gp.workers : std::min<uint32_t>(gp.num_work, (uint32_t)env.sm_count / cl);
-    const int      kern_out = (split > 1 || balanced) ? OUT_F32 : out;
+    const int      kern_out = split > 1 ? OUT_F32 : out; // (balanced: whole tiles go to C in its own type)
     cudaError_t    e;
     if (transposed) {
         switch (bn) {
-            case 16: e = launch_bn<16, 1, true>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, gp); break;
-            case 32: e = launch_bn<32, 1, true>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, gp); break;
-            case 64: e = launch_bn<64, 1, true>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, gp); break;
-            default: e = launch_bn<128, 1, true>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, gp); break;
+            case 16: e = launch_bn<16, 1, true>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, tmW, gp); break;
+            case 32: e = launch_bn<32, 1, true>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, tmW, gp); break;
+            case 64: e = launch_bn<64, 1, true>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, tmW, gp); break;
+            default: e = launch_bn<128, 1, true>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, tmW, gp); break;
         }
     } else if (cl == 2) {
-        if (bn <= 128) e = launch_bn<128, 2>(kern_out, units, env.pairs, 0, smem, stream, tmA, tmB, tmD, gp);
-        else if (bn <= 256) e = launch_bn<256, 2>(kern_out, units, env.pairs, 1, smem, stream, tmA, tmB, tmD, gp, gather ? &gmaps : nullptr);
-        else e = launch_bn<512, 2>(kern_out, units, env.pairs, 2, smem, stream, tmA, tmB, tmD, gp, gather ? &gmaps : nullptr);
+        if (bn <= 128) e = launch_bn<128, 2>(kern_out, units, env.pairs, 0, smem, stream, tmA, tmB, tmD, tmW, gp);
+        else if (bn <= 256) e = launch_bn<256, 2>(kern_out, units, env.pairs, 1, smem, stream, tmA, tmB, tmD, tmW, gp, gather ? &gmaps : nullptr);
+        else e = launch_bn<512, 2>(kern_out, units, env.pairs, 2, smem, stream, tmA, tmB, tmD, tmW, gp, gather ? &gmaps : nullptr);
     } else {
         switch (bn) {
-            case 16: e = launch_bn<16, 1>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, gp); break;
-            case 32: e = launch_bn<32, 1>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, gp); break;
-            case 64: e = launch_bn<64, 1>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, gp); break;
-            case 128: e = launch_bn<128, 1>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, gp); break;
-            default: e = launch_bn<256, 1>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, gp); break;
+            case 16: e = launch_bn<16, 1>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, tmW, gp); break;
+            case 32: e = launch_bn<32, 1>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, tmW, gp); break;
+            case 64: e = launch_bn<64, 1>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, tmW, gp); break;
+            case 128: e = launch_bn<128, 1>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, tmW, gp); break;
+            default: e = launch_bn<256, 1>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, tmW, gp); break;
         }
     }
     g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -1186,9 +1188,11 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
     }
 
     if (balanced) {
-        const uint64_t total4 = work * tile_rows * (uint64_t)(bn / 4);
-        const unsigned blocks = (unsigned)std::min<uint64_t>((total4 + 255) / 256, (uint64_t)env.sm_count * 8);
-        e = launch_streamk_reduce(out, blocks, stream, ws, v.d, gp, tile_rows, (uint32_t)bn);
+        e = cudaSuccess;
+        if (gp.workers > 1) { // one job per run boundary; each strides over one tile
+            const unsigned blocks = (unsigned)std::min<uint64_t>(((uint64_t)tile_rows * (bn / 4) + 255) / 256, 32);
+            e = launch_streamk_reduce(out, blocks, gp.workers - 1, stream, ws, v.d, gp, tile_rows, (uint32_t)bn);
+        }
         g_launches.fetch_add(1, std::memory_order_relaxed);
         if (ws_stream_ordered) cudaFreeAsync(ws, stream);
         if (e != cudaSuccess) return fail(B200_GEMM_ERR_CUDA, "balanced-schedule fix-up launch failed: %s", cudaGetErrorString(e));
@@ -1375,7 +1379,7 @@ extern "C" size_t b200_gemm_workspace_bytes(int types, size_t M, size_t N, size_
         const uint64_t tiles   = (uint64_t)((pl.v.M + tile_m - 1) / tile_m) * ((pl.v.N + pl.cfg.tile_n - 1) / pl.cfg.tile_n) * batch_count;
         const uint64_t upt     = ((pl.v.K + BLOCK_K - 1) / BLOCK_K + pl.kc - 1) / pl.kc;
         const uint64_t workers = std::min<uint64_t>(tiles * upt, (uint64_t)planning_sm_count(0) / cl);
-        return (size_t)(tiles + workers) * tile_m * pl.cfg.tile_n * sizeof(float);
+        return (size_t)(2 * workers) * tile_m * pl.cfg.tile_n * sizeof(float);
     }
     return pl.cfg.split_k > 1 ? batch_count * (size_t)pl.cfg.split_k * M * N * sizeof(float) : 0;
 }

@@ -156,16 +156,16 @@ def test_launch_plan_rules():
     lib = g.lib()
     for (m, n, k, t) in [(16, 8192, 8192, 1), (128, 8192, 8192, 1), (512, 512, 4096, 2), (8192, 8192, 8192, 3)]:
         p = g.plan(m, n, k, 0, 0, 1, types=t)
-        if p.split_k == 0:  # balanced schedule: one partial tile per segment, slots tile + worker
+        if p.split_k == 0:  # balanced schedule: at most two partial tiles per run
             upt = -(-(-(-k // 64)) // p.k_blocks_per_slot)
             workers = min(p.work_units * upt, 148 // p.cluster)
-            want = (p.work_units + workers) * p.tile_m * p.tile_n * 4
+            want = 2 * workers * p.tile_m * p.tile_n * 4
         else:
             want = p.split_k * m * n * 4 if p.split_k > 1 else 0
         assert lib.b200_gemm_workspace_bytes(t, m, n, k, 1, 0, 0, 1, None) == want
     # an explicit balanced configuration (split_k 0): 32 tiles of 128 x 256, 148 runs
     import ctypes
     cfg = g.GemmConfig(128, 256, 4, 1, 0, 0)
-    assert lib.b200_gemm_workspace_bytes(1, 128, 8192, 8192, 1, 0, 0, 1, ctypes.byref(cfg)) == (32 + 148) * 128 * 256 * 4
+    assert lib.b200_gemm_workspace_bytes(1, 128, 8192, 8192, 1, 0, 0, 1, ctypes.byref(cfg)) == 2 * 148 * 128 * 256 * 4
     cfg = g.GemmConfig(256, 512, 4, 2, 0, 0)  # no balanced form of the 512-wide tile
     assert lib.b200_gemm_workspace_bytes(3, 8192, 8192, 8192, 1, 0, 0, 1, ctypes.byref(cfg)) == 0

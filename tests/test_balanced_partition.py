@@ -1,7 +1,10 @@
 """The arithmetic of the balanced (stream-K) schedule, restated in Python and checked by
 exhaustion on small cases: the runs of `WorkCursor` (csrc/gemm_kernels.cuh) cover every K step
-of every tile exactly once, the workspace slot tile + worker is unique per segment, and the
-fix-up pass's closed form for "which workers touch tile t" names exactly the segments written."""
+of every tile exactly once; a run has at most two partial segments and their workspace slots
+(2 * worker for a segment that starts inside a tile, 2 * worker + 1 for one that ends inside a
+tile) never collide; and the fix-up pass (`streamk_reduce_kernel`) - one job per run boundary,
+the first boundary inside a tile owning it - visits exactly the tiles that were cut, with
+exactly the slots that were written, in K order."""
 import itertools
 
 import pytest
@@ -12,7 +15,7 @@ def run_start(worker, total, workers):
 
 
 def segments(worker, tiles, upt, workers):
-    """(tile, first K step, last K step (exclusive), slot) of each segment of one worker's run."""
+    """(tile, first K step, last K step (exclusive), partial, slot or None) of one worker's run."""
     total = tiles * upt
     nxt, end = run_start(worker, total, workers), run_start(worker + 1, total, workers)
     out = []
@@ -20,42 +23,62 @@ def segments(worker, tiles, upt, workers):
         tile = nxt // upt
         first = nxt - tile * upt
         last = min(upt, first + (end - nxt))
-        out.append((tile, first, last, tile + worker))
+        partial = first != 0 or last != upt
+        slot = (2 * worker + (0 if first != 0 else 1)) if partial else None
+        out.append((tile, first, last, partial, slot))
         nxt += last - first
     return out
 
 
-def fixup_workers(tile, upt, total, workers):
-    x0, x1 = tile * upt, tile * upt + upt - 1
-    w0 = ((x0 + 1) * workers + total - 1) // total - 1
-    w1 = ((x1 + 1) * workers + total - 1) // total - 1
-    return w0, w1
+def fixup_jobs(tiles, upt, workers):
+    """What the fix-up kernel does: {tile: [slots in the order they are added]}."""
+    total = tiles * upt
+    done = {}
+    for j in range(1, workers):
+        boundary = run_start(j, total, workers)
+        tile = boundary // upt
+        beg = tile * upt
+        if boundary == beg:
+            continue
+        if j > 1 and run_start(j - 1, total, workers) > beg:
+            continue
+        x0, x1 = beg, beg + upt - 1
+        w0 = ((x0 + 1) * workers + total - 1) // total - 1
+        w1 = ((x1 + 1) * workers + total - 1) // total - 1
+        assert tile not in done, "two jobs claim one tile"
+        done[tile] = [2 * w0 + 1] + [2 * w for w in range(w0 + 1, w1 + 1)]
+    return done
 
 
 @pytest.mark.parametrize("tiles,upt,sms", list(itertools.product([1, 2, 3, 7, 32, 64, 150, 513], [1, 2, 5, 16, 33, 128], [1, 3, 74, 148])))
-def test_runs_cover_every_step_once_and_fixup_finds_them(tiles, upt, sms):
+def test_runs_cover_every_step_once_and_fixup_finds_the_cut_tiles(tiles, upt, sms):
     total = tiles * upt
     workers = min(total, sms)
     seen = {}
     slots = {}
-    per_tile = {}
+    written = {}   # tile -> [(first K step, slot)] of its partial segments
+    whole = set()
     for w in range(workers):
-        steps = 0
-        for (tile, first, last, slot) in segments(w, tiles, upt, workers):
+        steps, partials = 0, 0
+        for (tile, first, last, partial, slot) in segments(w, tiles, upt, workers):
             assert 0 <= first < last <= upt
-            assert slot not in slots, "two segments share a workspace slot"
-            slots[slot] = (tile, w)
-            per_tile.setdefault(tile, []).append(w)
+            if partial:
+                partials += 1
+                assert slot not in slots, "two partial segments share a workspace slot"
+                slots[slot] = (tile, w)
+                written.setdefault(tile, []).append((first, slot))
+            else:
+                whole.add(tile)
             for k in range(first, last):
                 assert (tile, k) not in seen
                 seen[(tile, k)] = w
             steps += last - first
+        assert partials <= 2
         assert steps in (total // workers, total // workers + 1), "runs differ by more than one step"
     assert len(seen) == total
-    assert max(slots) <= tiles + workers - 2
-    for tile in range(tiles):
-        w0, w1 = fixup_workers(tile, upt, total, workers)
-        assert per_tile[tile] == list(range(w0, w1 + 1)), "the fix-up pass would add the wrong partial tiles"
-        # partials are added in ascending worker order = ascending K
-        firsts = [min(k for (t, k), w in seen.items() if t == tile and w == ww) for ww in range(w0, w1 + 1)]
-        assert firsts == sorted(firsts)
+    assert not slots or max(slots) < 2 * workers
+    assert whole.isdisjoint(written), "a tile is both stored whole and cut"
+    jobs = fixup_jobs(tiles, upt, workers)
+    assert set(jobs) == set(written), "the fix-up pass visits other tiles than the cut ones"
+    for tile, order in jobs.items():
+        assert order == [slot for _, slot in sorted(written[tile])], "wrong partials, or not in K order"

@@ -157,12 +157,14 @@ typedef struct b200_gemm_plan_info {
     int       tile_m;            /* kernel-view rows per tile: 128 x cluster, or the slab height (8..128) */
     int       tile_n;            /* kernel-view columns per tile */
     int       cluster;           /* CTAs per tile (1 or 2) */
-    int       split_k;           /* K partitions (> 1: a reduction pass follows) */
+    int       split_k;           /* K partitions (> 1: a reduction pass follows unless cluster_k is set) */
     int       slots;             /* ring depth */
     int       k_blocks_per_slot; /* 64-deep k-blocks staged per ring slot (1, 2 or 4) */
     int       raster;            /* tile-row band height (0: column sweep) */
     int       ctas;              /* CTAs launched (persistent: at most one per SM) */
     long long work_units;        /* tiles x K partitions x batch */
+    int       cluster_k;         /* 1: the K partitions of a tile are the CTAs of one thread-block cluster and are
+                                    summed through distributed shared memory: no workspace, no reduction pass */
 } b200_gemm_plan_info;
 int b200_gemm_plan(int types, size_t M, size_t N, size_t K, size_t batch_count, int layout_c,
                    int layout_a, int layout_b, int sm_count, b200_gemm_plan_info* out);

@@ -65,6 +65,8 @@ struct GemmParams {
     uint32_t ndst;         // gathering kernels: number of destination matrices every tile is stored to
     uint32_t dst_row0;     // gathering kernels: row and column of D(0, 0) within each destination
     uint32_t dst_col0;
+    uint32_t cluster_k;    // 1: the split_k K partitions of a tile are the CTAs of one cluster, summed through
+                           //    distributed shared memory (work items are tiles; the cluster rank is the partition)
 };
 
 // Destinations of a gathering kernel: one tensor map per copy of the full output matrix (this
@@ -216,20 +218,20 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, uint32_t t, uin
     }
 }
 
-__device__ __forceinline__ WorkCoord decode_work(const GemmParams& p, uint32_t w, int bn, int bm)
+__device__ __forceinline__ WorkCoord decode_work(const GemmParams& p, uint32_t w, int bn, int bm, uint32_t krank)
 {
     const uint32_t tiles = p.m_tiles * p.n_tiles;
     const uint32_t t     = w % tiles;
     const uint32_t r     = w / tiles;
-    const uint32_t split = r % p.split_k;
-    const uint32_t b     = r / p.split_k;
+    const uint32_t split = p.cluster_k ? krank : r % p.split_k;
+    const uint32_t b     = p.cluster_k ? r : r / p.split_k;
     uint32_t       m_idx, n_idx;
     tile_coords(p, t, m_idx, n_idx);
     WorkCoord c;
     c.m0    = m_idx * static_cast<uint32_t>(bm);
     c.n0    = n_idx * static_cast<uint32_t>(bn);
     c.z_in  = b;
-    c.z_out = b * p.split_k + split;
+    c.z_out = p.cluster_k ? b : b * p.split_k + split;
     c.kb0   = split * p.kb_per_split;
     c.kb1   = min(p.k_blocks, c.kb0 + p.kb_per_split);
     c.partial = 0u;
@@ -256,6 +258,7 @@ __device__ __forceinline__ WorkCoord decode_work(const GemmParams& p, uint32_t w
 struct WorkCursor {
     uint32_t next;  // plain: next work item; balanced: next K step of the run
     uint32_t end;   // balanced: end of the run
+    uint32_t krank; // cluster K partitions: this CTA's partition (its rank in the cluster)
 };
 
 __device__ __forceinline__ uint32_t run_start(const GemmParams& p, uint32_t worker)
@@ -263,9 +266,10 @@ __device__ __forceinline__ uint32_t run_start(const GemmParams& p, uint32_t work
     return static_cast<uint32_t>(static_cast<uint64_t>(worker) * p.total_units / p.workers);
 }
 
-__device__ __forceinline__ WorkCursor work_begin(const GemmParams& p, uint32_t unit)
+__device__ __forceinline__ WorkCursor work_begin(const GemmParams& p, uint32_t unit, uint32_t krank = 0u)
 {
     WorkCursor cur;
+    cur.krank = krank;
     if (p.balanced) {
         cur.next = run_start(p, unit);
         cur.end  = run_start(p, unit + 1u);
@@ -282,7 +286,7 @@ __device__ __forceinline__ bool work_next(const GemmParams& p, WorkCursor& cur, 
 {
     if (cur.next >= cur.end) return false;
     if (!p.balanced) {
-        c = decode_work(p, cur.next, bn, bm);
+        c = decode_work(p, cur.next, bn, bm, cur.krank);
         cur.next += units;
         return true;
     }
@@ -401,7 +405,7 @@ __device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits)
 // Edges: TMA zero-fills out-of-range loads (M, N and K tails) and clips stores.
 // No TMA load here uses cluster multicast.
 // ---------------------------------------------------------------------------------------------
-template <int BN, int OUT, int CL, bool TR, bool GATHER>
+template <int BN, int OUT, int CL, bool TR, bool GATHER, bool KS = false>
 __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUtensorMap& tmB,
                                                const CUtensorMap* tmDs, const CUtensorMap& tmW, const GemmParams& p)
 {
@@ -410,6 +414,8 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                   "BN must be 16, 32, 64, 128, 256 or 512");
     static_assert(CL == 1 || CL == 2, "cluster size must be 1 or 2");
     static_assert(!TR || CL == 1, "the transposed epilogue is a one-CTA variant");
+    static_assert(!KS || (CL == 1 && !TR && !GATHER && BN >= 128 && BN <= 256),
+                  "cluster K partitions: one-CTA staged tiles of 128 or 256 columns");
     // One MMA covers at most 256 columns: a 512-wide tile is two sub-tiles that share the A'
     // operand of every K slice (A' is staged once for 512 columns of output).
     constexpr int      UMMA_N       = BN > 256 ? 256 : BN;
@@ -444,8 +450,12 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
     const uint32_t lane   = tid & 31u;
     const uint32_t stages = p.stages;
     const uint32_t rank   = (CL == 2) ? ptx::cluster_ctarank() : 0u; // CTA rank in the pair
-    const uint32_t unit   = blockIdx.x / CL;                          // persistent worker index
-    const uint32_t units  = gridDim.x / CL;
+    // KS: the cluster is the worker, its rank the K partition (p.split_k CTAs per cluster).
+    const uint32_t krank  = KS ? ptx::cluster_ctarank() : 0u;
+    const uint32_t unit   = KS ? blockIdx.x / p.split_k : blockIdx.x / CL; // persistent worker index
+    const uint32_t units  = KS ? gridDim.x / p.split_k : gridDim.x / CL;
+    WorkCoord      ks_c{};        // KS: the one tile of this cluster (epilogue warps)
+    bool           ks_ok = false; // KS: accumulator complete
 
     // Bytes of A' per ring slot and slot pitch: compile-time for the staged epilogue; the
     // transposed variant stages p.bm (a multiple of 8, <= 128) rows of A' per slot.
@@ -521,7 +531,7 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
             bool     ok = true;
             const uint64_t pol_a = ptx::make_l2_policy(p.l2_hints & 3u);
             const uint64_t pol_b = ptx::make_l2_policy((p.l2_hints >> 2) & 3u);
-            WorkCursor cur = work_begin(p, unit);
+            WorkCursor cur = work_begin(p, unit, krank);
             WorkCoord  c;
             for (uint32_t w = unit; ok && work_next(p, cur, unit, units, wn, tile_m, c); w += units) {
                 const int32_t   am = static_cast<int32_t>(c.m0 + rank * BLOCK_M);
@@ -655,7 +665,7 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
             const uint32_t b_kstep = p.b_mn_major ? (2u * 1024u) >> 4 : (UMMA_K * 2u) >> 4;
             uint32_t       stage = 0, phase = 0, it = 0;
             bool           ok = true;
-            WorkCursor cur = work_begin(p, unit);
+            WorkCursor cur = work_begin(p, unit, krank);
             WorkCoord  c;
             for (; ok && work_next(p, cur, unit, units, wn, tile_m, c); ++it) {
                 if constexpr (NSUB == 2) {
@@ -795,8 +805,19 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
         uint32_t       it   = 0, nstore = 0;
         bool           ok   = true;
         const uint64_t pol_d = ptx::make_l2_policy((p.l2_hints >> 4) & 3u);
-        WorkCursor cur = work_begin(p, unit);
+        WorkCursor cur = work_begin(p, unit, krank);
         WorkCoord  c;
+        if constexpr (KS) {
+            // One tile per cluster: wait for this CTA's partial accumulator; the partials are
+            // summed after the cluster barrier below.
+            if (work_next(p, cur, unit, units, wn, tile_m, c)) {
+                ok = bounded_wait(ptx::smem_u32(&s_tfull[0]), 0u, &s_abort, p.status, ST_EPI_WAIT);
+                ok = __all_sync(0xffffffffu, ok);
+                ptx::tc_fence_after();
+                ks_c  = c;
+                ks_ok = ok;
+            }
+        } else
         for (; ok && work_next(p, cur, unit, units, wn, tile_m, c); ++it) {
             const uint32_t  buf    = it % NUM_ACC;
             const uint32_t  aphase = (it / NUM_ACC) & 1u;
@@ -941,6 +962,119 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
         if (lane == 0) ptx::tma_store_wait_read<0>();
     }
 
+    if constexpr (KS) {
+        // ------------------------------------------------------ sum of the cluster's K partitions
+        // Every CTA of the cluster holds an f32 partial of the same tile in TMEM.  The tile's
+        // 128-byte output chunks are dealt round-robin to the CTAs (chunk ch belongs to rank
+        // ch % split_k); each CTA sends the chunks it does not own to their owners' shared memory
+        // (the operand ring, free once every CTA's MMAs have retired: first barrier), and after the
+        // second barrier adds the partials of its own chunks in partition order - whichever CTA
+        // owns a chunk, the sum is ((p0 + p1) + p2) + ... - converts and stores them to C.  No
+        // workspace in global memory and no second kernel.  All threads of the cluster pass both
+        // barriers whatever happened before (a role that gave up a bounded wait included).
+        constexpr int      O_CH  = (OUT == OUT_F32) ? 32 : 64; // output columns per 128-byte chunk
+        constexpr int      NCH   = BN / O_CH;
+        constexpr uint32_t ROW_B = O_CH * 4u;                  // bytes of one row of an f32 chunk
+        constexpr uint32_t WSLOT = 32u * ROW_B;                // one warp's 32 rows of a chunk
+        const uint32_t ks   = p.split_k;
+        const uint32_t q    = warp & 3u;
+        const uint32_t tacc = tmem_base + ((q * 32u) << 16);
+        __syncwarp();
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+        if (warp >= 2 && ks_ok) {
+#pragma unroll 1
+            for (uint32_t ch = 0; ch < static_cast<uint32_t>(NCH); ++ch) {
+                const uint32_t owner = ch % ks;
+                if (owner == krank) continue;
+                // (within a warp's slot the 16-byte units are laid out [unit][lane]: every store and
+                // load instruction of the warp covers 512 contiguous bytes)
+                const uint32_t local  = ring + (((ch / ks) * ks + krank) * 4u + q) * WSLOT + lane * 16u;
+                const uint32_t remote = ptx::mapa_u32(local, owner);
+#pragma unroll
+                for (uint32_t h = 0; h < static_cast<uint32_t>(O_CH / 32); ++h) {
+                    uint32_t v[32];
+                    ptx::tmem_ld_32x32(tacc + ch * O_CH + h * 32u, v);
+                    ptx::tmem_ld_wait(v);
+#pragma unroll
+                    for (uint32_t j = 0; j < 8; ++j)
+                        ptx::st_cluster_v4(remote + (h * 8u + j) * 512u, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                }
+            }
+        }
+        __syncwarp();
+        ptx::cluster_arrive();
+        ptx::cluster_wait();
+        if (warp >= 2 && ks_ok) {
+            const uint32_t stg      = epi + q * 2u * EPI_BUF_BYTES;
+            const uint32_t row0     = ks_c.m0 + q * 32u;
+            const bool     row_live = row0 < p.M;
+            uint32_t       nstore   = 0;
+#pragma unroll 1
+            for (uint32_t ch = krank; ch < static_cast<uint32_t>(NCH); ch += ks) {
+                uint32_t own[O_CH];
+                float    acc[O_CH];
+#pragma unroll
+                for (uint32_t h = 0; h < static_cast<uint32_t>(O_CH / 32); ++h) {
+                    uint32_t t[32];
+                    ptx::tmem_ld_32x32(tacc + ch * O_CH + h * 32u, t);
+                    ptx::tmem_ld_wait(t);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) own[h * 32 + j] = t[j];
+                }
+#pragma unroll 1
+                for (uint32_t s = 0; s < ks; ++s) {
+                    if (s == krank) {
+#pragma unroll
+                        for (int j = 0; j < O_CH; ++j)
+                            acc[j] = (s == 0u) ? __uint_as_float(own[j]) : acc[j] + __uint_as_float(own[j]);
+                    } else {
+                        const uint32_t src = ring + (((ch / ks) * ks + s) * 4u + q) * WSLOT + lane * 16u;
+#pragma unroll
+                        for (uint32_t h = 0; h < static_cast<uint32_t>(O_CH / 32); ++h) {
+#pragma unroll
+                            for (uint32_t j = 0; j < 8; ++j) {
+                                uint32_t x0, x1, x2, x3;
+                                ptx::ld_shared_v4(src + (h * 8u + j) * 512u, x0, x1, x2, x3);
+                                const int at = h * 32 + 4 * j;
+                                acc[at]     = (s == 0u) ? __uint_as_float(x0) : acc[at] + __uint_as_float(x0);
+                                acc[at + 1] = (s == 0u) ? __uint_as_float(x1) : acc[at + 1] + __uint_as_float(x1);
+                                acc[at + 2] = (s == 0u) ? __uint_as_float(x2) : acc[at + 2] + __uint_as_float(x2);
+                                acc[at + 3] = (s == 0u) ? __uint_as_float(x3) : acc[at + 3] + __uint_as_float(x3);
+                            }
+                        }
+                    }
+                }
+                uint32_t v[32];
+                if constexpr (OUT == OUT_F32) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(acc[j]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = pack2<OUT>(__float_as_uint(acc[2 * j]), __float_as_uint(acc[2 * j + 1]));
+                }
+                const uint32_t col0 = ks_c.n0 + ch * O_CH;
+                if (row_live && col0 < p.N) {
+                    const uint32_t sbuf = stg + (nstore & 1u) * EPI_BUF_BYTES;
+                    if (lane == 0) ptx::tma_store_wait_read<1>();
+                    __syncwarp();
+                    const uint32_t rowaddr = sbuf + lane * 128u;
+#pragma unroll
+                    for (uint32_t j = 0; j < 8; ++j)
+                        st_shared_v4(rowaddr + ((j ^ (lane & 7u)) << 4), v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::tma_store_3d(&tmD, sbuf, col0, row0, ks_c.z_out, ptx::make_l2_policy((p.l2_hints >> 4) & 3u));
+                        ptx::tma_store_commit();
+                    }
+                    ++nstore;
+                }
+            }
+            if (lane == 0) ptx::tma_store_wait_read<0>();
+        }
+    }
+
     // ---------------------------------------------------------------------- tail
     ptx::tc_fence_before();
     __syncthreads();
@@ -977,6 +1111,17 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
                             const __grid_constant__ GatherMaps dst, const GemmParams p)
 {
     gemm_umma_body<BN, OUT, CL, false, true>(tmA, tmB, dst.m, dst.m[0], p);
+}
+
+// The same GEMM with a tile's K partitions spread over the CTAs of a cluster (cluster size =
+// p.split_k, one tile per cluster) and summed through distributed shared memory.
+template <int BN, int OUT>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+    gemm_umma_ksplit_kernel(const __grid_constant__ CUtensorMap tmA,
+                            const __grid_constant__ CUtensorMap tmB,
+                            const __grid_constant__ CUtensorMap tmD, const GemmParams p)
+{
+    gemm_umma_body<BN, OUT, 1, false, false, true>(tmA, tmB, &tmD, tmD, p);
 }
 
 // ---------------------------------------------------------------------------------------------

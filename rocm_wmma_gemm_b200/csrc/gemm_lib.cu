@@ -207,6 +207,11 @@ static cudaError_t set_smem_attr_one()
             e = cudaFuncSetAttribute(gemm_umma_gather_kernel<BN, OUT, CL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)gemm_smem_bytes(BN, CL, max_stages(BN, CL)));
     }
+    if constexpr (CL == 1 && BN >= 128 && BN <= 256) {
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemm_umma_ksplit_kernel<BN, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)gemm_smem_bytes(BN, CL, max_stages(BN, CL)));
+    }
     return e;
 }
 
@@ -699,6 +704,32 @@ static cudaError_t launch_bn(int out, uint32_t units_wanted, PairCache* pairs, i
     }
 }
 
+// One cluster of `split` CTAs per tile, the CTAs being the tile's K partitions.
+template <int BN>
+static cudaError_t launch_ksplit(int out, uint32_t tiles, uint32_t split, uint32_t smem, cudaStream_t s, const CUtensorMap& a,
+                                 const CUtensorMap& b, const CUtensorMap& d, const GemmParams& gp)
+{
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim            = dim3(tiles * split);
+    lc.blockDim           = dim3(GEMM_THREADS);
+    lc.dynamicSmemBytes   = smem;
+    lc.stream             = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id               = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = split;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs                                           = attr;
+    lc.numAttrs                                        = 2;
+    switch (out) {
+        case OUT_F32: return cudaLaunchKernelEx(&lc, gemm_umma_ksplit_kernel<BN, OUT_F32>, a, b, d, gp);
+        case OUT_F16: return cudaLaunchKernelEx(&lc, gemm_umma_ksplit_kernel<BN, OUT_F16>, a, b, d, gp);
+        default: return cudaLaunchKernelEx(&lc, gemm_umma_ksplit_kernel<BN, OUT_BF16>, a, b, d, gp);
+    }
+}
+
 template <class TIn, class TOut>
 static cudaError_t launch_generic(const Problem& p, cudaStream_t s)
 {
@@ -772,6 +803,7 @@ struct LaunchPlan {
     bool             slot       = false; // one-CTA kernel with kc k-blocks per ring slot
     bool             k4d        = false; // K-major operands through the 4-D (chunked K) maps
     bool             balanced   = false; // balanced (stream-K) schedule: runs of K steps cut across tiles
+    bool             cluster_k  = false; // the K partitions of a tile are one cluster's CTAs, summed on chip (no workspace)
     View             v{};
     b200_gemm_config cfg{};
     uint32_t         bm = BLOCK_M, kc = 1, kb_per_split = 0;
@@ -907,6 +939,29 @@ static int make_plan(const Problem& p, const b200_gemm_config* user_cfg, int sm_
     }
     if (transposed) cfg.stages = slab_max_stages((int)bm, cfg.tile_n, (int)kc);
     else if (slot && (narrow || kc > 1)) cfg.stages = slot_max_stages(cfg.tile_n, (int)kc);
+    // K partitions of the one-CTA 128- and 256-column tiles: up to 4 of them form a thread-block
+    // cluster and add their partial tiles through distributed shared memory, received in the
+    // operand ring (which must hold one f32 tile's worth of chunks).  No workspace, no reduction
+    // kernel, and the output is written once in its own type.  One tile per cluster, so the path
+    // is taken when all clusters are resident at once (a second wave of clusters costs more than
+    // the reduction pass of the persistent kernel; 7/8 of the SMs allows for GPCs whose SM count
+    // is not a multiple of the cluster size); clusters of 5 to 8 CTAs measured no faster than the
+    // reduction pass.
+    static const int cluster_k_env = [] { // B200_GEMM_CLUSTER_SPLITK = 0 / 1 forces the workspace / the cluster path (profiling)
+        const char* e = getenv("B200_GEMM_CLUSTER_SPLITK");
+        return (e && *e) ? atoi(e) : -1;
+    }();
+    if (slot && !narrow && !transposed && !balanced && cfg.split_k > 1 && cfg.split_k <= 4 && bm == (uint32_t)BLOCK_M &&
+        (cfg.tile_n == 128 || cfg.tile_n == 256) && cluster_k_env != 0) {
+        const uint32_t o_ch   = out_is_f32(p.types) ? 32u : 64u;
+        const uint32_t nch    = (uint32_t)cfg.tile_n / o_ch;
+        const uint32_t split  = (uint32_t)cfg.split_k;
+        const uint64_t need   = (uint64_t)((nch + split - 1) / split) * split * 4u * 32u * o_ch * 4u;
+        const uint64_t ring   = (uint64_t)cfg.stages * kc * stage_bytes(cfg.tile_n, 1);
+        const uint64_t tiles  = (uint64_t)((v.M + BLOCK_M - 1) / BLOCK_M) * ((v.N + cfg.tile_n - 1) / cfg.tile_n) * p.batch;
+        const uint64_t room   = (uint64_t)sm_count / split * 7 / 8; // clusters resident at once, conservatively
+        pl.cluster_k          = ring >= need && (tiles <= room || cluster_k_env == 1);
+    }
     *out = pl;
     return B200_GEMM_OK;
 }
@@ -1006,6 +1061,7 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
     const uint32_t          kc           = pl.kc;
     const uint32_t          kb_per_split = pl.kb_per_split;
     const bool              balanced     = pl.balanced;
+    const bool              cluster_k    = pl.cluster_k;
 
     const int      bn   = cfg.tile_n;
     const int      out  = out_kind(p.types);
@@ -1029,8 +1085,9 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
     gp.kb_per_split = kb_per_split;
     gp.group_m      = (uint32_t)(cfg.raster & ~B200_GEMM_RASTER_SNAKE);
     gp.snake        = (cfg.raster & B200_GEMM_RASTER_SNAKE) ? 1u : 0u;
-    const uint64_t work = (uint64_t)gp.batch * split * gp.m_tiles * gp.n_tiles;
-    if (work > 0x7fffffffull) return fail(B200_GEMM_ERR_BAD_SIZE, "too many tiles (%llu)", (unsigned long long)work);
+    gp.cluster_k    = cluster_k ? 1u : 0u;
+    const uint64_t work = (uint64_t)gp.batch * (cluster_k ? 1u : split) * gp.m_tiles * gp.n_tiles;
+    if (work * (cluster_k ? split : 1u) > 0x7fffffffull) return fail(B200_GEMM_ERR_BAD_SIZE, "too many tiles (%llu)", (unsigned long long)work);
     gp.num_work   = (uint32_t)work;
     // Balanced schedule: `work` tiles of units_per_tile K steps each, cut into `workers` runs.
     const uint32_t tile_rows = slot ? bm : (uint32_t)BLOCK_M * cl;
@@ -1081,9 +1138,9 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
     // (balanced: one tile_rows x bn partial tile per partial segment, two slots per worker)
     const size_t ws_slots = balanced ? 2 * (size_t)gp.workers : 0;
     const size_t ws_bytes = balanced ? ws_slots * tile_rows * bn * sizeof(float)
-                                     : (split > 1 ? (size_t)p.batch * split * v.M * v.N * sizeof(float) : 0);
+                                     : (split > 1 && !cluster_k ? (size_t)p.batch * split * v.M * v.N * sizeof(float) : 0);
     bool         ws_stream_ordered = false;
-    if (split > 1 || balanced) {
+    if ((split > 1 && !cluster_k) || balanced) {
         if (!transposed && v.N % 4) return fail(B200_GEMM_ERR_BAD_CONFIG, "split_k needs N %% 4 == 0 in the kernel view");
         if (fixed) {
             if (ws_bytes > env.fixed_ws_bytes)
@@ -1118,9 +1175,9 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
     tmW = tmA; // only the balanced schedule uses it; any valid descriptor will do otherwise
     if (st == B200_GEMM_OK && transposed) {
         tmD    = tmA; // not used by the transposed epilogue; any valid descriptor will do
-        gp.out = split > 1 ? static_cast<void*>(ws) : v.d;
+        gp.out = split > 1 ? static_cast<void*>(ws) : v.d; // (transposed plans never use cluster K partitions)
     } else if (st == B200_GEMM_OK) {
-        if (split > 1)
+        if (split > 1 && !cluster_k)
             st = encode_map(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ws, v.N, v.M, (uint64_t)p.batch * split, 32, 32);
         else if (out == OUT_F32)
             st = encode_map(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, v.d, v.N, v.M, p.batch, 32, 32);
@@ -1158,9 +1215,12 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
     const uint32_t smem     = transposed ? slab_smem_bytes((int)bm, bn, (int)kc, cfg.stages)
                               : (slot ? slot_smem_bytes(bn, (int)kc, cfg.stages) : gemm_smem_bytes(compiled_width(bn), (int)cl, cfg.stages));
     const uint32_t units    = balanced ? gp.workers : std::min<uint32_t>(gp.num_work, (uint32_t)env.sm_count / cl);
-    const int      kern_out = split > 1 ? OUT_F32 : out; // (balanced: whole tiles go to C in its own type)
+    const int      kern_out = (split > 1 && !cluster_k) ? OUT_F32 : out; // (balanced: whole tiles go to C in its own type)
     cudaError_t    e;
-    if (transposed) {
+    if (cluster_k) {
+        if (bn == 128) e = launch_ksplit<128>(out, gp.num_work, split, smem, stream, tmA, tmB, tmD, gp);
+        else e = launch_ksplit<256>(out, gp.num_work, split, smem, stream, tmA, tmB, tmD, gp);
+    } else if (transposed) {
         switch (bn) {
             case 16: e = launch_bn<16, 1, true>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, tmW, gp); break;
             case 32: e = launch_bn<32, 1, true>(kern_out, units, nullptr, 0, smem, stream, tmA, tmB, tmD, tmW, gp); break;
@@ -1196,7 +1256,7 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
         g_launches.fetch_add(1, std::memory_order_relaxed);
         if (ws_stream_ordered) cudaFreeAsync(ws, stream);
         if (e != cudaSuccess) return fail(B200_GEMM_ERR_CUDA, "balanced-schedule fix-up launch failed: %s", cudaGetErrorString(e));
-    } else if (split > 1) {
+    } else if (split > 1 && !cluster_k) {
         const uint64_t mn     = (uint64_t)v.M * v.N;
         const uint64_t total4 = mn * p.batch / 4;
         const unsigned blocks = (unsigned)std::min<uint64_t>((total4 + 255) / 256, (uint64_t)env.sm_count * 8);
@@ -1381,7 +1441,7 @@ extern "C" size_t b200_gemm_workspace_bytes(int types, size_t M, size_t N, size_
         const uint64_t workers = std::min<uint64_t>(tiles * upt, (uint64_t)planning_sm_count(0) / cl);
         return (size_t)(2 * workers) * tile_m * pl.cfg.tile_n * sizeof(float);
     }
-    return pl.cfg.split_k > 1 ? batch_count * (size_t)pl.cfg.split_k * M * N * sizeof(float) : 0;
+    return (pl.cfg.split_k > 1 && !pl.cluster_k) ? batch_count * (size_t)pl.cfg.split_k * M * N * sizeof(float) : 0;
 }
 
 extern "C" int b200_gemm_plan(int types, size_t M, size_t N, size_t K, size_t batch_count, int layout_c,
@@ -1416,8 +1476,9 @@ extern "C" int b200_gemm_plan(int types, size_t M, size_t N, size_t K, size_t ba
     out->k_blocks_per_slot = (int)pl.kc;
     out->raster            = pl.cfg.raster;
     const uint64_t k_steps = pl.balanced ? work * ((((uint64_t)pl.v.K + BLOCK_K - 1) / BLOCK_K + pl.kc - 1) / pl.kc) : work;
-    out->ctas              = (int)(cl * std::min<uint64_t>(k_steps, (uint64_t)sms / cl));
+    out->ctas              = pl.cluster_k ? (int)work : (int)(cl * std::min<uint64_t>(k_steps, (uint64_t)sms / cl));
     out->work_units        = (long long)work;
+    out->cluster_k         = pl.cluster_k ? 1 : 0;
     return B200_GEMM_OK;
 }
 

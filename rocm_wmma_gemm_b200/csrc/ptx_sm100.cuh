@@ -269,6 +269,19 @@ __device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t cta_rank)
     return r;
 }
 
+// 16-byte store into the shared memory of a CTA of this cluster (`addr` from mapa_u32), and the
+// matching load from this CTA's own.
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d)
+                 : "memory");
+}
+
+__device__ __forceinline__ void ld_shared_v4(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d)
+{
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr) : "memory");
+}
+
 __device__ __forceinline__ void cluster_arrive()
 {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");

@@ -161,7 +161,7 @@ def test_launch_plan_rules():
             workers = min(p.work_units * upt, 148 // p.cluster)
             want = 2 * workers * p.tile_m * p.tile_n * 4
         else:
-            want = p.split_k * m * n * 4 if p.split_k > 1 else 0
+            want = p.split_k * m * n * 4 if p.split_k > 1 and not p.cluster_k else 0
         assert lib.b200_gemm_workspace_bytes(t, m, n, k, 1, 0, 0, 1, None) == want
     # an explicit balanced configuration (split_k 0): 32 tiles of 128 x 256, 148 runs
     import ctypes

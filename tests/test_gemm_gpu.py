@@ -189,6 +189,52 @@ def test_balanced_schedule_batched_and_rejected():
         gpu_gemm(3, A[: M * K], B[: K * N], M, N, K, 0, 0, 1, config=g.GemmConfig(256, 512, 4, 2, 0, 0))
 
 
+CLUSTER_K = [
+    # tile_n, split_k | M, N, K
+    (256, 4, 128, 2048, 4096),          # 8 tiles x 4 partitions: the skinny streaming case
+    (128, 2, 384, 1160, 1280 + 64),     # ragged N and K, two k-blocks per ring slot
+    (256, 3, 200, 1000, 3008),          # three partitions (cluster of 3), ragged rows and columns
+    (128, 4, 512, 512, 4096),           # 16 tiles x 4
+    (256, 2, 136, 520, 192),            # three k-blocks over two partitions (2 + 1)
+]
+
+
+@pytest.mark.parametrize("tile_n,split,M,N,K", CLUSTER_K, ids=[f"{c[0]}-split{c[1]}-{c[2]}x{c[3]}x{c[4]}" for c in CLUSTER_K])
+def test_cluster_k_partitions(tile_n, split, M, N, K):
+    """K partitions of a one-CTA tile as the CTAs of one thread-block cluster, summed through
+    distributed shared memory (no workspace, no reduction pass): all type pairs and layouts
+    against the oracle, bit-identical from run to run, and no workspace asked for."""
+    lib = g.lib()
+    for types in range(4):
+        bf16 = types >= 2
+        for (la, lb, lc) in LAYOUTS:
+            cfg = g.GemmConfig(128, tile_n, 4, 1, split, 0)
+            A, B = seeded(M, N, K, la, lb, bf16)
+            ref = oracle.hgemm(types, A, B, M, N, K, lc, la, lb)
+            got = gpu_gemm(types, A, B, M, N, K, lc, la, lb, config=cfg)
+            check_parity(types, got, ref, K, SIGMA_UNIFORM, M, N, lc)
+            if (la, lb, lc) in ((0, 1, 0), (1, 0, 1)):
+                import ctypes
+                assert lib.b200_gemm_workspace_bytes(types, M, N, K, 1, lc, la, lb, ctypes.byref(cfg)) == 0, "expected the cluster path"
+                again = gpu_gemm(types, A, B, M, N, K, lc, la, lb, config=cfg)
+                assert np.array_equal(got.view(np.uint8), again.view(np.uint8))
+    assert g.device_status() == 0
+
+
+def test_cluster_k_partitions_batched_and_table():
+    M, N, K, batch = 192, 320, 2048, 3
+    A = np.concatenate([oracle.init_matrix(M, K, 0, True)[(np.arange(M * K) + 97 * b) % (M * K)] for b in range(batch)])
+    B = np.concatenate([oracle.init_matrix(K, N, 1, True)[(np.arange(K * N) + 31 * b) % (K * N)] for b in range(batch)])
+    got = gpu_gemm(2, A, B, M, N, K, 0, 0, 1, batch=batch, config=g.GemmConfig(128, 128, 4, 1, 4, 0))
+    for b in range(batch):
+        ref = oracle.hgemm(2, A[b * M * K:(b + 1) * M * K], B[b * K * N:(b + 1) * K * N], M, N, K, 0, 0, 1)
+        check_parity(2, got[b * M * N:(b + 1) * M * N], ref, K, SIGMA_UNIFORM, M, N, 0)
+    # more tiles than clusters fit at once: the persistent kernel with its workspace is used
+    import ctypes
+    cfg = g.GemmConfig(128, 128, 4, 1, 2, 0)
+    assert g.lib().b200_gemm_workspace_bytes(2, 4096, 4096, 256, 1, 0, 0, 1, ctypes.byref(cfg)) == 2 * 4096 * 4096 * 4
+
+
 def test_all_layouts_agree():
     """The same logical product through all 8 layouts gives the same C (tight tolerance: the
     products are identical, only tile shapes and operand roles differ)."""

@@ -39,7 +39,7 @@ def _both(L, types, A, B, M, N, K, lc, la, lb, cfg):
 def test_static_workspace_matches_allocating_entry_point_twice(types):
     L = g.loader()
     bf16 = types >= 2
-    cfg = g.GemmConfig(128, 128, 4, 1, 4, 0)  # four K partitions -> scratch is used
+    cfg = g.GemmConfig(128, 128, 4, 1, 4, 0)  # four K partitions: scratch is used by call 1 (operand swap); call 2 sums them inside clusters
     # Call 1, then call 2 with a different shape, layout and data: the workspace still holds
     # call 1's partials when call 2 starts.
     cases = [(64, 1024, 4096, 0, 0, 1), (128, 768, 2048 + 64, 1, 1, 0)]

@@ -518,11 +518,21 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
     const uint32_t tmem_base = s_tmem_base;
     // Programmatic dependent launch, both directions.  This grid may have been scheduled while
     // the kernel before it in the stream was still draining: everything above touched only this
-    // CTA's shared memory and TMEM; global memory is first used below, after the wait.  And the
-    // kernel after this one (the split-K reduction, or the next GEMM) may be scheduled as SMs
-    // free up; it waits for this grid to complete before it reads or writes anything.
-    ptx::grid_dep_wait();
+    // CTA's shared memory and TMEM.  Each thread that touches global memory waits for the kernel
+    // before this one right before its first access (the producer before its first TMA load, the
+    // epilogue threads before their first store), so the work decode, the address arithmetic and
+    // the first barrier operations of every role run while that kernel drains - about a
+    // microsecond of every launch otherwise.  The MMA thread touches no global memory.  The
+    // kernel after this one (a reduction pass, or the next GEMM) may be scheduled as SMs free
+    // up; it waits for this grid to complete before it reads or writes anything.
     ptx::grid_dep_launch();
+    bool dep_waited = false;
+    auto dep_wait = [&]() {
+        if (!dep_waited) {
+            ptx::grid_dep_wait();
+            dep_waited = true;
+        }
+    };
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -559,6 +569,7 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                         const uint32_t sb  = sa + kc * a_bytes;
                         const uint32_t bar = ptx::smem_u32(&s_full[stage]);
                         ptx::mbar_expect_tx(bar, pitch);
+                        dep_wait();
                         if (p.a_mn_major == 0u) {
                             if (p.k4d) ptx::tma_load_4d(sa, &tmA, bar, 0, am, kb, c.z_in, pol_a);
                             else ptx::tma_load_3d(sa, &tmA, bar, k0, am, c.z_in, pol_a);
@@ -605,6 +616,7 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                     } else {
                         ptx::mbar_expect_tx(bar, step_bytes);
                     }
+                    dep_wait();
                     if (p.a_mn_major == 0u) {
                         tma_load<CL>(sa, &tmA, bar, k0, am, c.z_in, pol_a);
                     } else {
@@ -848,6 +860,7 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                 // whatever follows the slab in shared memory): never stored.
                 const uint32_t i      = c.m0 + q * 32u + lane;
                 const bool     i_live = (q * 32u + lane) < p.bm && i < p.M;
+                dep_wait();
 #pragma unroll 1
                 for (int ch = 0; ch < (BN + 31) / 32; ++ch) {
                     uint32_t v[32];
@@ -931,6 +944,7 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                     ptx::fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
+                        dep_wait();
                         if constexpr (GATHER) {
                             // The tile goes to every copy of the full matrix (this GPU's and its
                             // peers', over NVLink) at the slab's offset: the all-gather of the
@@ -1065,6 +1079,7 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                     ptx::fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
+                        dep_wait();
                         ptx::tma_store_3d(&tmD, sbuf, col0, row0, ks_c.z_out, ptx::make_l2_policy((p.l2_hints >> 4) & 3u));
                         ptx::tma_store_commit();
                     }

@@ -233,6 +233,11 @@ static cudaError_t set_smem_attr_narrow_one()
     if (e == cudaSuccess && BN < 64)
         e = cudaFuncSetAttribute(gemm_umma_kernel<BN, OUT, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)gemm_smem_bytes(BN, 1, max_stages(BN, 1, false), false));
+    if constexpr (BN >= 64) {
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(gemm_umma_ksplit_kernel<BN, OUT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)SLAB_SMEM_LIMIT);
+    }
     return e;
 }
 
@@ -705,7 +710,7 @@ static cudaError_t launch_bn(int out, uint32_t units_wanted, PairCache* pairs, i
 }
 
 // One cluster of `split` CTAs per tile, the CTAs being the tile's K partitions.
-template <int BN>
+template <int BN, bool TR = false>
 static cudaError_t launch_ksplit(int out, uint32_t tiles, uint32_t split, uint32_t smem, cudaStream_t s, const CUtensorMap& a,
                                  const CUtensorMap& b, const CUtensorMap& d, const GemmParams& gp)
 {
@@ -724,9 +729,9 @@ static cudaError_t launch_ksplit(int out, uint32_t tiles, uint32_t split, uint32
     lc.attrs                                           = attr;
     lc.numAttrs                                        = 2;
     switch (out) {
-        case OUT_F32: return cudaLaunchKernelEx(&lc, gemm_umma_ksplit_kernel<BN, OUT_F32>, a, b, d, gp);
-        case OUT_F16: return cudaLaunchKernelEx(&lc, gemm_umma_ksplit_kernel<BN, OUT_F16>, a, b, d, gp);
-        default: return cudaLaunchKernelEx(&lc, gemm_umma_ksplit_kernel<BN, OUT_BF16>, a, b, d, gp);
+        case OUT_F32: return cudaLaunchKernelEx(&lc, gemm_umma_ksplit_kernel<BN, OUT_F32, TR>, a, b, d, gp);
+        case OUT_F16: return cudaLaunchKernelEx(&lc, gemm_umma_ksplit_kernel<BN, OUT_F16, TR>, a, b, d, gp);
+        default: return cudaLaunchKernelEx(&lc, gemm_umma_ksplit_kernel<BN, OUT_BF16, TR>, a, b, d, gp);
     }
 }
 
@@ -826,6 +831,10 @@ static int make_plan(const Problem& p, const b200_gemm_config* user_cfg, int sm_
     // split_k == 0 asks for the balanced (stream-K) schedule, which keeps the plain orientation.
     bool  balanced   = cfg.split_k == 0;
     bool& transposed = pl.transposed;
+    static const int cluster_k_env = [] { // B200_GEMM_CLUSTER_SPLITK = 0 / 1 forces the workspace / the cluster form of split-K (profiling)
+        const char* e = getenv("B200_GEMM_CLUSTER_SPLITK");
+        return (e && *e) ? atoi(e) : -1;
+    }();
     if (!balanced && v.M <= 64 && v.N >= 128 && operands_tma_ok(p, v) && reinterpret_cast<uintptr_t>(v.d) % 16 == 0 &&
         ((size_t)v.M * v.N) % 4 == 0) {
         std::swap(v.a, v.b);
@@ -900,6 +909,27 @@ static int make_plan(const Problem& p, const b200_gemm_config* user_cfg, int sm_
             bm          = best_bm;
             cfg.split_k = 1;
         }
+        // Transposed problems whose small operand has 64 or more rows: every slab re-reads that
+        // operand from L2, and with 147 slabs those re-reads, not HBM, bound the kernel.  Two K
+        // partitions per slab, as the two CTAs of a cluster, halve them: twice the slab height,
+        // half the K range per CTA, partial slabs summed through distributed shared memory.
+        // One slab per cluster, all clusters resident at once.
+        const uint32_t k_blocks = (v.K + BLOCK_K - 1) / BLOCK_K;
+        if (transposed && cluster_k_env != 0 && cfg.tile_n >= 64 && k_blocks >= 32) {
+            const uint32_t units = sms / 2;
+            for (uint32_t cand = step; cand <= (uint32_t)BLOCK_M; cand += step) {
+                const uint64_t tiles = (uint64_t)((v.M + cand - 1) / cand) * p.batch;
+                if (tiles > units) continue;
+                // (the ring, which receives the partials, fills the CTA's shared memory whatever the
+                // slab height: it always holds the 32 or 64 KiB of one partial slab)
+                if (tiles * 10u >= units * 8u) {
+                    bm           = cand;
+                    cfg.split_k  = 2;
+                    pl.cluster_k = true;
+                }
+                break; // the lowest slab height that fits one wave
+            }
+        }
     }
     uint32_t& kb_per_split = pl.kb_per_split;
     legalize(cfg, v, &kb_per_split);
@@ -947,10 +977,6 @@ static int make_plan(const Problem& p, const b200_gemm_config* user_cfg, int sm_
     // the reduction pass of the persistent kernel; 7/8 of the SMs allows for GPCs whose SM count
     // is not a multiple of the cluster size); clusters of 5 to 8 CTAs measured no faster than the
     // reduction pass.
-    static const int cluster_k_env = [] { // B200_GEMM_CLUSTER_SPLITK = 0 / 1 forces the workspace / the cluster path (profiling)
-        const char* e = getenv("B200_GEMM_CLUSTER_SPLITK");
-        return (e && *e) ? atoi(e) : -1;
-    }();
     if (slot && !narrow && !transposed && !balanced && cfg.split_k > 1 && cfg.split_k <= 4 && bm == (uint32_t)BLOCK_M &&
         (cfg.tile_n == 128 || cfg.tile_n == 256) && cluster_k_env != 0) {
         const uint32_t o_ch   = out_is_f32(p.types) ? 32u : 64u;
@@ -1175,7 +1201,7 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
     tmW = tmA; // only the balanced schedule uses it; any valid descriptor will do otherwise
     if (st == B200_GEMM_OK && transposed) {
         tmD    = tmA; // not used by the transposed epilogue; any valid descriptor will do
-        gp.out = split > 1 ? static_cast<void*>(ws) : v.d; // (transposed plans never use cluster K partitions)
+        gp.out = (split > 1 && !cluster_k) ? static_cast<void*>(ws) : v.d;
     } else if (st == B200_GEMM_OK) {
         if (split > 1 && !cluster_k)
             st = encode_map(&tmD, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, ws, v.N, v.M, (uint64_t)p.batch * split, 32, 32);
@@ -1217,7 +1243,10 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
     const uint32_t units    = balanced ? gp.workers : std::min<uint32_t>(gp.num_work, (uint32_t)env.sm_count / cl);
     const int      kern_out = (split > 1 && !cluster_k) ? OUT_F32 : out; // (balanced: whole tiles go to C in its own type)
     cudaError_t    e;
-    if (cluster_k) {
+    if (cluster_k && transposed) {
+        if (bn == 64) e = launch_ksplit<64, true>(out, gp.num_work, split, smem, stream, tmA, tmB, tmD, gp);
+        else e = launch_ksplit<128, true>(out, gp.num_work, split, smem, stream, tmA, tmB, tmD, gp);
+    } else if (cluster_k) {
         if (bn == 128) e = launch_ksplit<128>(out, gp.num_work, split, smem, stream, tmA, tmB, tmD, gp);
         else e = launch_ksplit<256>(out, gp.num_work, split, smem, stream, tmA, tmB, tmD, gp);
     } else if (transposed) {

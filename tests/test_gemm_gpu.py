@@ -221,6 +221,29 @@ def test_cluster_k_partitions(tile_n, split, M, N, K):
     assert g.device_status() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(64, 2368, 2048 + 64), (48, 4096, 2048), (64, 1000, 4096)])
+def test_cluster_k_partitions_transposed(M, N, K):
+    """Skinny problems with 33 to 64 rows: the operand-swapped slab kernel with two K partitions
+    per slab as the two CTAs of a cluster (interleaved K steps, partial slabs summed through
+    distributed shared memory, transposing stores).  All type pairs and layouts against the
+    oracle; the plan reports the form."""
+    p = g.plan(M, N, K, 0, 0, 1, types=1, sm_count=148)
+    assert p.kernel == 3 and p.cluster_k == 1 and p.split_k == 2 and p.ctas == p.work_units <= 148
+    for types in range(4):
+        bf16 = types >= 2
+        for (la, lb, lc) in LAYOUTS:
+            # the skinny dimension is M for a row-major C and N for a column-major one
+            m, n = (M, N) if lc == 0 else (N, M)
+            A, B = seeded(m, n, K, la, lb, bf16)
+            ref = oracle.hgemm(types, A, B, m, n, K, lc, la, lb)
+            got = gpu_gemm(types, A, B, m, n, K, lc, la, lb)
+            check_parity(types, got, ref, K, SIGMA_UNIFORM, m, n, lc)
+            if (la, lb) == (0, 1):
+                again = gpu_gemm(types, A, B, m, n, K, lc, la, lb)
+                assert np.array_equal(got.view(np.uint8), again.view(np.uint8))
+    assert g.device_status() == 0
+
+
 def test_cluster_k_partitions_batched_and_table():
     M, N, K, batch = 192, 320, 2048, 3
     A = np.concatenate([oracle.init_matrix(M, K, 0, True)[(np.arange(M * K) + 97 * b) % (M * K)] for b in range(batch)])

@@ -58,10 +58,11 @@ struct GemmParams {
     uint32_t k4d;          // one-CTA kernels: K-major operands use the 4-D (chunked K) maps
     uint32_t snake;        // raster: odd bands (odd columns of a column sweep) run backwards
     uint32_t l2_hints;     // L2 eviction priorities: bits [0,2) A', [2,4) B', [4,6) D (L2_HINT_*)
-    uint32_t balanced;     // 1: balanced (stream-K) schedule, see WorkCursor; outputs are f32 partial tiles
+    uint32_t balanced;     // 1: balanced (stream-K) schedule, see WorkCursor
     uint32_t units_per_tile; // balanced: K steps (ring slots of kc k-blocks) per tile
-    uint32_t workers;      // balanced: runs the work is cut into (= persistent CTAs / CTA pairs)
-    uint32_t total_units;  // balanced: tiles x units_per_tile
+    uint32_t workers;      // balanced: runs the cut tiles' K loops are divided into (<= persistent CTAs / CTA pairs)
+    uint32_t total_units;  // balanced: sk_tiles x units_per_tile
+    uint32_t sk_tiles;     // balanced: tiles [0, sk_tiles) are cut into runs; tiles [sk_tiles, num_work) are dealt whole
     uint32_t ndst;         // gathering kernels: number of destination matrices every tile is stored to
     uint32_t dst_row0;     // gathering kernels: row and column of D(0, 0) within each destination
     uint32_t dst_col0;
@@ -244,21 +245,26 @@ __device__ __forceinline__ WorkCoord decode_work(const GemmParams& p, uint32_t w
 // Plain schedule: work items unit, unit + units, ... of the num_work (batch x K partition x
 // tile) items.
 //
-// Balanced schedule (stream-K; the reference's roadmap names it, README.md:202): the tiles'
-// K loops are laid end to end - tile 0's K steps, then tile 1's, ... - and that line of
-// total_units steps is cut into `workers` equal runs, one per worker, wherever the cuts fall.
-// A worker walks its run segment by segment (a segment = the part of one tile's K loop inside
-// the run), so every SM gets the same number of K steps whatever the tile count.  A segment
-// that covers a tile's whole K loop stores the tile to C like the plain schedule does.  A
-// partial segment leaves an f32 partial tile in the workspace: a run has at most two of them,
-// its first (it starts inside a tile: slot 2 * worker) and its last (it ends inside a tile:
-// slot 2 * worker + 1); the fix-up pass (streamk_reduce_kernel) adds a split tile's partials in
+// Balanced schedule (stream-K; the reference's roadmap names it, README.md:202).  Whole waves
+// of tiles need no balancing, so only the tiles of the incomplete wave - sk_tiles = tiles mod
+// workers, or all of them when there are fewer tiles than workers - are cut: their K loops are
+// laid end to end - tile 0's K steps, then tile 1's, ... - and that line of total_units steps
+// is cut into `workers` equal runs, one per worker, wherever the cuts fall.  A worker first
+// walks its run segment by segment (a segment = the part of one tile's K loop inside the run)
+// and then takes whole tiles sk_tiles + worker, sk_tiles + worker + grid, ... like the plain
+// schedule: every SM gets the same number of K steps whatever the tile count, and the cut
+// tiles' partials are written early in the kernel, not at its end.  A segment that covers a
+// tile's whole K loop stores the tile to C like the plain schedule does.  A partial segment
+// leaves an f32 partial tile in the workspace: a run has at most two of them, its first (it
+// starts inside a tile: slot 2 * worker) and its last (it ends inside a tile: slot
+// 2 * worker + 1); the fix-up pass (streamk_reduce_kernel) adds a split tile's partials in
 // K order and writes C.  No CTA waits for another.
 // ---------------------------------------------------------------------------------------------
 struct WorkCursor {
     uint32_t next;  // plain: next work item; balanced: next K step of the run
     uint32_t end;   // balanced: end of the run
     uint32_t krank; // cluster K partitions: this CTA's partition (its rank in the cluster)
+    uint32_t dp;    // balanced: next whole tile of this worker
 };
 
 __device__ __forceinline__ uint32_t run_start(const GemmParams& p, uint32_t worker)
@@ -270,9 +276,12 @@ __device__ __forceinline__ WorkCursor work_begin(const GemmParams& p, uint32_t u
 {
     WorkCursor cur;
     cur.krank = krank;
+    cur.dp = 0u;
     if (p.balanced) {
-        cur.next = run_start(p, unit);
-        cur.end  = run_start(p, unit + 1u);
+        const bool has_run = unit < p.workers;
+        cur.next = has_run ? run_start(p, unit) : 0u;
+        cur.end  = has_run ? run_start(p, unit + 1u) : 0u;
+        cur.dp   = p.sk_tiles + unit;
     } else {
         cur.next = unit;
         cur.end  = p.num_work;
@@ -284,10 +293,25 @@ __device__ __forceinline__ WorkCursor work_begin(const GemmParams& p, uint32_t u
 __device__ __forceinline__ bool work_next(const GemmParams& p, WorkCursor& cur, uint32_t unit, uint32_t units,
                                           int bn, int bm, WorkCoord& c)
 {
-    if (cur.next >= cur.end) return false;
     if (!p.balanced) {
+        if (cur.next >= cur.end) return false;
         c = decode_work(p, cur.next, bn, bm, cur.krank);
         cur.next += units;
+        return true;
+    }
+    if (cur.next >= cur.end) { // the run is done: whole tiles, round-robin over the grid
+        if (cur.dp >= p.num_work) return false;
+        const uint32_t tiles = p.m_tiles * p.n_tiles;
+        uint32_t       m_idx, n_idx;
+        tile_coords(p, cur.dp % tiles, m_idx, n_idx);
+        c.m0      = m_idx * static_cast<uint32_t>(bm);
+        c.n0      = n_idx * static_cast<uint32_t>(bn);
+        c.z_in    = cur.dp / tiles;
+        c.z_out   = c.z_in;
+        c.partial = 0u;
+        c.kb0     = 0u;
+        c.kb1     = p.k_blocks;
+        cur.dp += units;
         return true;
     }
     const uint32_t tile  = cur.next / p.units_per_tile;          // over batch x tiles

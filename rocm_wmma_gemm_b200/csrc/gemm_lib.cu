@@ -543,14 +543,20 @@ static b200_gemm_config resolve_config(const Problem& p, const b200_gemm_config*
 //   time = waves x k-blocks x cycles per k-block + exposed epilogue + launch (+ reduction pass)
 // with cycles per k-block the larger of the tensor-pipe time and the per-slot issue work of the
 // producer / MMA threads, measured on this design.  Sizes with an entry are never touched.
-static void adapt_config(b200_gemm_config& c, const View& v, size_t batch, int sms)
+static void adapt_config(b200_gemm_config& c, const View& v, size_t batch, int sms, int out_chunk)
 {
     struct Shape {
         int    tm, tn, cl;
         double cyc_per_kb, epilogue;
     };
-    static const Shape ladder[5] = {{256, 512, 2, 1060, 5500},
+    // (224 / 192 / 160: run-time widths of the 256-column pair kernel, for column counts that
+    // 256 cuts into a nearly empty last wave - 2304^3: 81 tiles on 74 pairs; they need a K-major
+    // B' and whole 128-byte output chunks)
+    static const Shape ladder[8] = {{256, 512, 2, 1060, 5500},
                                     {256, 256, 2, 540, 2700},
+                                    {256, 224, 2, 480, 2400},
+                                    {256, 192, 2, 415, 2100},
+                                    {256, 160, 2, 355, 1800},
                                     {128, 256, 1, 570, 2700},
                                     {128, 128, 1, 500, 1400},
                                     {128, 64, 1, 400, 800}};
@@ -560,7 +566,13 @@ static void adapt_config(b200_gemm_config& c, const View& v, size_t batch, int s
         const uint64_t slots = (uint64_t)(sms / t.cl);
         const uint64_t waves = (tiles + slots - 1) / slots;
         const double   kb    = (double)((k_blocks + split - 1) / split);
-        double         cyc   = (double)waves * kb * t.cyc_per_kb + t.epilogue + 3000.0;
+        // One-CTA tiles stage 1.5 to 2 times the operand bytes per FLOP of a CTA pair; with every
+        // SM loading at once (more than one wave of tiles) the L2-to-SM path paces them:
+        // 3000^3 on 128 x 256 tiles 63.9 us, on 256 x 256 pair tiles 44.7 us.
+        const double   per_kb = t.cyc_per_kb * ((t.cl == 1 && tiles > slots) ? 1.4 : 1.0);
+        // (a pair kernel's launch and set-up cost more: cluster scheduling, one k-block per ring
+        // slot; 1536^3 runs 9.4 us on 128 x 128 tiles and 12.0 us on one wave of pair tiles)
+        double         cyc   = (double)waves * kb * per_kb + t.epilogue + 3000.0 + (t.cl == 2 ? 2500.0 : 0.0);
         if (split > 1) cyc += 3000.0 + (double)v.M * v.N * batch * 4.0 * (split + 1) / 4000.0; // partials: ~4 KB per cycle
         return cyc;
     };
@@ -571,6 +583,7 @@ static void adapt_config(b200_gemm_config& c, const View& v, size_t batch, int s
     const Shape* bt   = nullptr;
     int          bs   = 1;
     for (const Shape& t : ladder) {
+        if (t.tn != compiled_width(t.tn) && (v.b_mn || t.tn % out_chunk)) continue;
         for (int split : {1, 2, 4, 8, 16}) {
             if (split > 1 && (v.N % 4 != 0 || (uint32_t)split * 4 > k_blocks)) continue;
             const double m = model(t, split);
@@ -800,6 +813,22 @@ static cudaError_t launch_streamk_reduce(int out, unsigned blocks, unsigned jobs
     }
 }
 
+// Geometry of the balanced schedule for `tiles` tiles of `upt` K steps on `slots` persistent
+// workers (CTAs or CTA pairs): whole waves of tiles are dealt round-robin; the tiles of the
+// incomplete wave (all tiles when there are fewer than workers) are cut into `runs` equal runs
+// of K steps.  `grid` = workers launched.
+struct BalancedGeometry {
+    uint64_t sk_tiles, runs, grid;
+};
+static BalancedGeometry balanced_geometry(uint64_t tiles, uint64_t upt, uint64_t slots)
+{
+    BalancedGeometry g;
+    g.sk_tiles = tiles <= slots ? tiles : tiles % slots;
+    g.runs     = std::max<uint64_t>(1, std::min<uint64_t>(g.sk_tiles * upt, slots));
+    g.grid     = tiles >= slots ? slots : g.runs;
+    return g;
+}
+
 // Everything the launch path decides before it touches the GPU.
 struct LaunchPlan {
     bool             generic    = false; // TMA cannot address the problem: CUDA-core kernel
@@ -848,7 +877,7 @@ static int make_plan(const Problem& p, const b200_gemm_config* user_cfg, int sm_
         return B200_GEMM_OK;
     }
 
-    if (!tuned && !balanced) adapt_config(cfg, v, p.batch, sm_count);
+    if (!tuned && !balanced) adapt_config(cfg, v, p.batch, sm_count, out_is_f32(p.types) ? 32 : 64);
     // Narrow kernel views (at most 64 columns) run on the narrow one-CTA variants whatever
     // tile the table names: tile_n is the smallest compiled width that covers N (an MN-major
     // B' is loaded in 64-row boxes, so it needs 64) and the ring is as deep as fits.
@@ -1117,15 +1146,19 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
     gp.num_work   = (uint32_t)work;
     // Balanced schedule: `work` tiles of units_per_tile K steps each, cut into `workers` runs.
     const uint32_t tile_rows = slot ? bm : (uint32_t)BLOCK_M * cl;
-    gp.balanced = gp.units_per_tile = gp.workers = gp.total_units = 0;
+    gp.balanced = gp.units_per_tile = gp.workers = gp.total_units = gp.sk_tiles = 0;
+    uint32_t balanced_grid = 0;
     if (balanced) {
-        const uint64_t upt   = (gp.k_blocks + kc - 1) / kc;
-        const uint64_t total = work * upt;
+        const uint64_t         upt = (gp.k_blocks + kc - 1) / kc;
+        const BalancedGeometry g   = balanced_geometry(work, upt, (uint64_t)env.sm_count / cl);
+        const uint64_t         total = g.sk_tiles * upt;
         if (total > 0x7fffffffull) return fail(B200_GEMM_ERR_BAD_SIZE, "too many K steps for the balanced schedule (%llu)", (unsigned long long)total);
         gp.balanced       = 1;
         gp.units_per_tile = (uint32_t)upt;
+        gp.sk_tiles       = (uint32_t)g.sk_tiles;
         gp.total_units    = (uint32_t)total;
-        gp.workers        = (uint32_t)std::min<uint64_t>(total, (uint64_t)env.sm_count / cl);
+        gp.workers        = (uint32_t)g.runs;
+        balanced_grid     = (uint32_t)g.grid;
     }
     const int umma_n = bn > 256 ? 256 : bn; // columns per MMA; a 512-wide tile is two sub-tiles
     gp.a_mn_major = v.a_mn ? 1u : 0u;
@@ -1240,7 +1273,7 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
 
     const uint32_t smem     = transposed ? slab_smem_bytes((int)bm, bn, (int)kc, cfg.stages)
                               : (slot ? slot_smem_bytes(bn, (int)kc, cfg.stages) : gemm_smem_bytes(compiled_width(bn), (int)cl, cfg.stages));
-    const uint32_t units    = balanced ? gp.workers : std::min<uint32_t>(gp.num_work, (uint32_t)env.sm_count / cl);
+    const uint32_t units    = balanced ? balanced_grid : std::min<uint32_t>(gp.num_work, (uint32_t)env.sm_count / cl);
     const int      kern_out = (split > 1 && !cluster_k) ? OUT_F32 : out; // (balanced: whole tiles go to C in its own type)
     cudaError_t    e;
     if (cluster_k && transposed) {
@@ -1278,7 +1311,7 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
 
     if (balanced) {
         e = cudaSuccess;
-        if (gp.workers > 1) { // one job per run boundary; each strides over one tile
+        if (gp.workers > 1 && gp.sk_tiles > 0) { // one job per run boundary; each strides over one tile
             const unsigned blocks = (unsigned)std::min<uint64_t>(((uint64_t)tile_rows * (bn / 4) + 255) / 256, 32);
             e = launch_streamk_reduce(out, blocks, gp.workers - 1, stream, ws, v.d, gp, tile_rows, (uint32_t)bn);
         }
@@ -1467,8 +1500,8 @@ extern "C" size_t b200_gemm_workspace_bytes(int types, size_t M, size_t N, size_
         const uint32_t tile_m  = pl.slot ? pl.bm : (uint32_t)BLOCK_M * cl;
         const uint64_t tiles   = (uint64_t)((pl.v.M + tile_m - 1) / tile_m) * ((pl.v.N + pl.cfg.tile_n - 1) / pl.cfg.tile_n) * batch_count;
         const uint64_t upt     = ((pl.v.K + BLOCK_K - 1) / BLOCK_K + pl.kc - 1) / pl.kc;
-        const uint64_t workers = std::min<uint64_t>(tiles * upt, (uint64_t)planning_sm_count(0) / cl);
-        return (size_t)(2 * workers) * tile_m * pl.cfg.tile_n * sizeof(float);
+        const uint64_t runs    = balanced_geometry(tiles, upt, (uint64_t)planning_sm_count(0) / cl).runs;
+        return (size_t)(2 * runs) * tile_m * pl.cfg.tile_n * sizeof(float);
     }
     return (pl.cfg.split_k > 1 && !pl.cluster_k) ? batch_count * (size_t)pl.cfg.split_k * M * N * sizeof(float) : 0;
 }
@@ -1504,8 +1537,9 @@ extern "C" int b200_gemm_plan(int types, size_t M, size_t N, size_t K, size_t ba
     out->slots             = pl.cfg.stages;
     out->k_blocks_per_slot = (int)pl.kc;
     out->raster            = pl.cfg.raster;
-    const uint64_t k_steps = pl.balanced ? work * ((((uint64_t)pl.v.K + BLOCK_K - 1) / BLOCK_K + pl.kc - 1) / pl.kc) : work;
-    out->ctas              = pl.cluster_k ? (int)work : (int)(cl * std::min<uint64_t>(k_steps, (uint64_t)sms / cl));
+    const uint64_t upt     = (((uint64_t)pl.v.K + BLOCK_K - 1) / BLOCK_K + pl.kc - 1) / pl.kc;
+    const uint64_t workers = pl.balanced ? balanced_geometry(work, upt, (uint64_t)sms / cl).grid : std::min<uint64_t>(work, (uint64_t)sms / cl);
+    out->ctas              = pl.cluster_k ? (int)work : (int)(cl * workers);
     out->work_units        = (long long)work;
     out->cluster_k         = pl.cluster_k ? 1 : 0;
     return B200_GEMM_OK;

@@ -1,5 +1,6 @@
 """The arithmetic of the balanced (stream-K) schedule, restated in Python and checked by
-exhaustion on small cases: the runs of `WorkCursor` (csrc/gemm_kernels.cuh) cover every K step
+exhaustion on small cases.  Whole waves of tiles are dealt round-robin; the tiles of the
+incomplete wave (all tiles when there are fewer than workers) are cut into runs, and for them: the runs of `WorkCursor` (csrc/gemm_kernels.cuh) cover every K step
 of every tile exactly once; a run has at most two partial segments and their workspace slots
 (2 * worker for a segment that starts inside a tile, 2 * worker + 1 for one that ends inside a
 tile) never collide; and the fix-up pass (`streamk_reduce_kernel`) - one job per run boundary,
@@ -82,3 +83,40 @@ def test_runs_cover_every_step_once_and_fixup_finds_the_cut_tiles(tiles, upt, sm
     assert set(jobs) == set(written), "the fix-up pass visits other tiles than the cut ones"
     for tile, order in jobs.items():
         assert order == [slot for _, slot in sorted(written[tile])], "wrong partials, or not in K order"
+
+
+def geometry(tiles, upt, slots):
+    """`balanced_geometry` of csrc/gemm_lib.cu."""
+    sk = tiles if tiles <= slots else tiles % slots
+    runs = max(1, min(sk * upt, slots))
+    grid = slots if tiles >= slots else runs
+    return sk, runs, grid
+
+
+@pytest.mark.parametrize("tiles,upt,slots", list(itertools.product([1, 2, 7, 73, 74, 75, 148, 160, 256, 300, 513], [1, 4, 32, 128], [1, 3, 74, 148])))
+def test_whole_waves_round_robin_and_the_rest_in_runs(tiles, upt, slots):
+    sk, runs, grid = geometry(tiles, upt, slots)
+    assert 0 <= sk <= tiles and (tiles - sk) % slots == 0 or tiles <= slots
+    assert 1 <= runs <= grid <= slots or sk == 0
+    seen = {}
+    for unit in range(grid):
+        steps = 0
+        if unit < runs:  # the worker's run over the cut tiles (WorkCursor: next / end)
+            for (tile, first, last, partial, slot) in (segments(unit, sk, upt, runs) if sk else []):
+                assert tile < sk
+                for k in range(first, last):
+                    assert (tile, k) not in seen
+                    seen[(tile, k)] = unit
+                steps += last - first
+        t = sk + unit     # then whole tiles (WorkCursor: dp)
+        while t < tiles:
+            for k in range(upt):
+                assert (t, k) not in seen
+                seen[(t, k)] = unit
+            steps += upt
+            t += grid
+    assert len(seen) == tiles * upt, "a K step of some tile is never computed"
+    # every worker's load is within one K step of the others' when the tiles outnumber the workers
+    if tiles >= slots and sk * upt >= slots:
+        per = [sum(1 for v in seen.values() if v == u) for u in range(grid)]
+        assert max(per) - min(per) <= 1

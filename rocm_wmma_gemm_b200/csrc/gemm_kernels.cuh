@@ -438,8 +438,8 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                   "BN must be 16, 32, 64, 128, 256 or 512");
     static_assert(CL == 1 || CL == 2, "cluster size must be 1 or 2");
     static_assert(!TR || CL == 1, "the transposed epilogue is a one-CTA variant");
-    static_assert(!KS || (CL == 1 && !GATHER && ((!TR && BN >= 128 && BN <= 256) || (TR && BN >= 32 && BN <= 128))),
-                  "cluster K partitions: one-CTA staged tiles of 128 or 256 columns, transposed slabs of 32 to 128");
+    static_assert(!KS || (CL == 1 && !GATHER && ((!TR && BN >= 128 && BN <= 256) || (TR && BN <= 128))),
+                  "cluster K partitions: one-CTA staged tiles of 128 or 256 columns, transposed slabs of up to 128");
     // One MMA covers at most 256 columns: a 512-wide tile is two sub-tiles that share the A'
     // operand of every K slice (A' is staged once for 512 columns of output).
     constexpr int      UMMA_N       = BN > 256 ? 256 : BN;
@@ -1020,7 +1020,7 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
         // barriers whatever happened before (a role that gave up a bounded wait included).
         // (the transposed epilogue stores element by element: its chunks are 32 f32 columns)
         constexpr int      O_CH  = (TR || OUT == OUT_F32) ? 32 : 64; // output columns per chunk
-        constexpr int      NCH   = BN / O_CH;
+        constexpr int      NCH   = TR ? (BN + 31) / 32 : BN / O_CH; // (a 16-column slab is one chunk, half of it unused)
         constexpr uint32_t ROW_B = O_CH * 4u;                  // bytes of one row of an f32 chunk
         constexpr uint32_t WSLOT = 32u * ROW_B;                // one warp's 32 rows of a chunk
         const uint32_t ks   = p.split_k;

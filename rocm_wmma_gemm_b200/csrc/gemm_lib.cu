@@ -233,11 +233,9 @@ static cudaError_t set_smem_attr_narrow_one()
     if (e == cudaSuccess && BN < 64)
         e = cudaFuncSetAttribute(gemm_umma_kernel<BN, OUT, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)gemm_smem_bytes(BN, 1, max_stages(BN, 1, false), false));
-    if constexpr (BN >= 64) {
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(gemm_umma_ksplit_kernel<BN, OUT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)SLAB_SMEM_LIMIT);
-    }
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_umma_ksplit_kernel<BN, OUT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)SLAB_SMEM_LIMIT);
     return e;
 }
 
@@ -938,25 +936,62 @@ static int make_plan(const Problem& p, const b200_gemm_config* user_cfg, int sm_
             bm          = best_bm;
             cfg.split_k = 1;
         }
-        // Transposed problems whose small operand has 64 or more rows: every slab re-reads that
-        // operand from L2, and with 147 slabs those re-reads, not HBM, bound the kernel.  Two K
-        // partitions per slab, as the two CTAs of a cluster, halve them: twice the slab height,
-        // half the K range per CTA, partial slabs summed through distributed shared memory.
-        // One slab per cluster, all clusters resident at once.
+        // Transposed problems: two or four K partitions per slab, as the CTAs of a cluster
+        // (taller slabs, a shorter K range per CTA, partial slabs summed through distributed
+        // shared memory; one slab per cluster, all clusters resident at once), when a small model
+        // of a CTA's time says so.  Three things can bound a slab kernel:
+        //   the MMA thread   the MMA spans 128 rows whatever the slab height, so a CTA issues
+        //                    4 MMAs per k-block of its K range however few rows it streams: about
+        //                    275 cycles per k-block (16 x 4096 x 14336 on 32-row slabs: 32 us,
+        //                    against the vendor GEMM's 22);
+        //   HBM              the slab's bytes at the CTA's share of ~3.3 KB per cycle (and at most
+        //                    ~38 B per cycle for one SM);
+        //   L2 to SM         slab + small operand, ~43 B per cycle per SM with every SM loading
+        //                    (64 x 8192 x 8192 on 147 slabs: 281 MB, the bound there).
+        // K partitions shorten the first and the third.
         const uint32_t k_blocks = (v.K + BLOCK_K - 1) / BLOCK_K;
-        if (transposed && cluster_k_env != 0 && cfg.tile_n >= 64 && k_blocks >= 32) {
-            const uint32_t units = sms / 2;
-            for (uint32_t cand = step; cand <= (uint32_t)BLOCK_M; cand += step) {
-                const uint64_t tiles = (uint64_t)((v.M + cand - 1) / cand) * p.batch;
-                if (tiles > units) continue;
-                // (the ring, which receives the partials, fills the CTA's shared memory whatever the
-                // slab height: it always holds the 32 or 64 KiB of one partial slab)
-                if (tiles * 10u >= units * 8u) {
-                    bm           = cand;
-                    cfg.split_k  = 2;
-                    pl.cluster_k = true;
+        if (transposed && cluster_k_env != 0 && k_blocks >= 32) {
+            auto cta_cycles = [&](uint32_t rows, uint32_t split, uint64_t tiles) {
+                const double kb     = (double)((k_blocks + split - 1) / split);
+                const double active = (double)std::min<uint64_t>(tiles * split, sms);
+                const double bytes  = (double)rows * kb * BLOCK_K * 2.0;
+                const double mma    = kb * 275.0;
+                const double hbm    = std::max(bytes * active / 3300.0, bytes / 38.0);
+                const double l2     = ((double)rows + cfg.tile_n) * kb * BLOCK_K * 2.0 / 43.0;
+                return std::max(mma, std::max(hbm, l2));
+            };
+            double   best = 1e300;
+            uint32_t best_rows = 0, best_split = 1;
+            if (cfg.split_k == 1) { // the slabs chosen above, no K partitions
+                const uint64_t tiles = (uint64_t)((v.M + bm - 1) / bm) * p.batch;
+                best      = (double)((tiles + sms - 1) / sms) * cta_cycles(bm, 1, tiles);
+                best_rows = bm;
+            }
+            for (uint32_t split : {2u, 4u}) {
+                // clusters resident at once: every pair of SMs hosts a cluster of two; clusters of
+                // four do not tile GPCs whose SM count is not a multiple of four (37 of them took
+                // two waves), so 7/8 of the SMs are counted on
+                const uint32_t units = split == 2u ? sms / 2u : sms / split * 7u / 8u;
+                for (uint32_t cand = step; cand <= (uint32_t)BLOCK_M; cand += step) {
+                    const uint64_t tiles = (uint64_t)((v.M + cand - 1) / cand) * p.batch;
+                    if (tiles > units) continue;
+                    if (tiles * 10u >= units * 8u) {
+                        const double c = cta_cycles(cand, split, tiles) + 2500.0;
+                        if (c < best * 0.97) {
+                            best       = c;
+                            best_rows  = cand;
+                            best_split = split;
+                        }
+                    }
+                    break; // the lowest slab height that fits one wave
                 }
-                break; // the lowest slab height that fits one wave
+            }
+            if (best_split > 1) {
+                // (the ring, which receives the partials, fills the CTA's shared memory whatever
+                // the slab height: it always holds the 16 to 64 KiB of the partial slabs)
+                bm           = best_rows;
+                cfg.split_k  = (int)best_split;
+                pl.cluster_k = true;
             }
         }
     }
@@ -1277,8 +1312,12 @@ static int launch_gemm(const Problem& p, cudaStream_t stream, const b200_gemm_co
     const int      kern_out = (split > 1 && !cluster_k) ? OUT_F32 : out; // (balanced: whole tiles go to C in its own type)
     cudaError_t    e;
     if (cluster_k && transposed) {
-        if (bn == 64) e = launch_ksplit<64, true>(out, gp.num_work, split, smem, stream, tmA, tmB, tmD, gp);
-        else e = launch_ksplit<128, true>(out, gp.num_work, split, smem, stream, tmA, tmB, tmD, gp);
+        switch (bn) {
+            case 16: e = launch_ksplit<16, true>(out, gp.num_work, split, smem, stream, tmA, tmB, tmD, gp); break;
+            case 32: e = launch_ksplit<32, true>(out, gp.num_work, split, smem, stream, tmA, tmB, tmD, gp); break;
+            case 64: e = launch_ksplit<64, true>(out, gp.num_work, split, smem, stream, tmA, tmB, tmD, gp); break;
+            default: e = launch_ksplit<128, true>(out, gp.num_work, split, smem, stream, tmA, tmB, tmD, gp); break;
+        }
     } else if (cluster_k) {
         if (bn == 128) e = launch_ksplit<128>(out, gp.num_work, split, smem, stream, tmA, tmB, tmD, gp);
         else e = launch_ksplit<256>(out, gp.num_work, split, smem, stream, tmA, tmB, tmD, gp);

@@ -221,14 +221,14 @@ def test_cluster_k_partitions(tile_n, split, M, N, K):
     assert g.device_status() == 0
 
 
-@pytest.mark.parametrize("M,N,K", [(64, 2368, 2048 + 64), (48, 4096, 2048), (64, 1000, 4096)])
+@pytest.mark.parametrize("M,N,K", [(64, 2368, 2048 + 64), (48, 4096, 2048), (64, 1000, 4096), (16, 4096, 4096 + 64), (24, 2048, 8192)])
 def test_cluster_k_partitions_transposed(M, N, K):
-    """Skinny problems with 33 to 64 rows: the operand-swapped slab kernel with two K partitions
-    per slab as the two CTAs of a cluster (interleaved K steps, partial slabs summed through
+    """Skinny problems: the operand-swapped slab kernel with two or four K partitions per slab
+    as the CTAs of a cluster (two: interleaved K steps; partial slabs summed through
     distributed shared memory, transposing stores).  All type pairs and layouts against the
     oracle; the plan reports the form."""
     p = g.plan(M, N, K, 0, 0, 1, types=1, sm_count=148)
-    assert p.kernel == 3 and p.cluster_k == 1 and p.split_k == 2 and p.ctas == p.work_units <= 148
+    assert p.kernel == 3 and p.cluster_k == 1 and p.split_k in (2, 3, 4) and p.ctas == p.work_units <= 148
     for types in range(4):
         bf16 = types >= 2
         for (la, lb, lc) in LAYOUTS:

@@ -559,19 +559,35 @@ static void adapt_config(b200_gemm_config& c, const View& v, size_t batch, int s
                                     {128, 128, 1, 500, 1400},
                                     {128, 64, 1, 400, 800}};
     const uint32_t k_blocks = (v.K + BLOCK_K - 1) / BLOCK_K;
+    const double out_bytes = out_chunk == 32 ? 4.0 : 2.0;
     auto model = [&](const Shape& t, int split) {
-        const uint64_t tiles = (uint64_t)((v.M + t.tm - 1) / t.tm) * ((v.N + t.tn - 1) / t.tn) * batch * (uint64_t)split;
+        const uint64_t tiles1 = (uint64_t)((v.M + t.tm - 1) / t.tm) * ((v.N + t.tn - 1) / t.tn) * batch;
+        const uint64_t tiles = tiles1 * (uint64_t)split;
         const uint64_t slots = (uint64_t)(sms / t.cl);
         const uint64_t waves = (tiles + slots - 1) / slots;
         const double   kb    = (double)((k_blocks + split - 1) / split);
+        // K partitions of the one-CTA 128- and 256-column tiles are summed inside a cluster when
+        // all clusters fit at once (make_plan's rule): no workspace, no second kernel; the
+        // exchange, barriers and sum cost ~3000 cycles + (split - 1) / split of an f32 tile per
+        // CTA at ~8 B per cycle (timeline of 128 x 8192 x 8192: 14k cycles for 128 x 256 x 4,
+        // 6k for 128 x 128 x 2).
+        const bool in_cluster = split >= 2 && split <= 4 && t.cl == 1 && t.tn >= 128 && tiles1 <= (uint64_t)(sms / split * 7 / 8);
+        // A CTA drains its part of a tile at ~19.5 B per cycle (12.5 in a pair): with a short K
+        // loop that, not the main loop, is the time of a tile (8192 x 8192 x 128: 31.6 us on
+        // 128 x 256 tiles, 42.8 us on 256 x 256 pair tiles).
+        const double   drain = 128.0 * (t.tn > 256 ? 512.0 : (double)t.tn) * out_bytes / (t.cl == 2 ? 12.5 : 19.5);
         // One-CTA tiles stage 1.5 to 2 times the operand bytes per FLOP of a CTA pair; with every
         // SM loading at once (more than one wave of tiles) the L2-to-SM path paces them:
         // 3000^3 on 128 x 256 tiles 63.9 us, on 256 x 256 pair tiles 44.7 us.
         const double   per_kb = t.cyc_per_kb * ((t.cl == 1 && tiles > slots) ? 1.4 : 1.0);
         // (a pair kernel's launch and set-up cost more: cluster scheduling, one k-block per ring
         // slot; 1536^3 runs 9.4 us on 128 x 128 tiles and 12.0 us on one wave of pair tiles)
-        double         cyc   = (double)waves * kb * per_kb + t.epilogue + 3000.0 + (t.cl == 2 ? 2500.0 : 0.0);
-        if (split > 1) cyc += 3000.0 + (double)v.M * v.N * batch * 4.0 * (split + 1) / 4000.0; // partials: ~4 KB per cycle
+        // (+ ~600 cycles per tile of work decode and accumulator hand-over: 4096 x 4096 x 64 runs
+        // 10.0 us on 512 tiles of 128 x 256 and 16.7 us on 2048 tiles of 128 x 64)
+        const double   tile  = (split == 1 ? std::max(kb * per_kb, drain) : kb * per_kb) + 600.0;
+        double         cyc   = (double)waves * tile + t.epilogue + 3000.0 + (t.cl == 2 ? 2500.0 : 0.0);
+        if (in_cluster) cyc += 3000.0 + 128.0 * t.tn * 4.0 * (split - 1) / split / 8.0;
+        else if (split > 1) cyc += 7000.0 + (double)v.M * v.N * batch * 4.0 * (split + 1) / 4000.0; // a second kernel; partials: ~4 KB per cycle
         return cyc;
     };
     double current = -1.0;
@@ -582,7 +598,7 @@ static void adapt_config(b200_gemm_config& c, const View& v, size_t batch, int s
     int          bs   = 1;
     for (const Shape& t : ladder) {
         if (t.tn != compiled_width(t.tn) && (v.b_mn || t.tn % out_chunk)) continue;
-        for (int split : {1, 2, 4, 8, 16}) {
+        for (int split : {1, 2, 3, 4, 8, 16}) {
             if (split > 1 && (v.N % 4 != 0 || (uint32_t)split * 4 > k_blocks)) continue;
             const double m = model(t, split);
             if (m < best) {

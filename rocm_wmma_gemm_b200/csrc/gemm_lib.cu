@@ -552,9 +552,9 @@ static void adapt_config(b200_gemm_config& c, const View& v, size_t batch, int s
     // B' and whole 128-byte output chunks)
     static const Shape ladder[8] = {{256, 512, 2, 1060, 5500},
                                     {256, 256, 2, 540, 2700},
-                                    {256, 224, 2, 480, 2400},
-                                    {256, 192, 2, 415, 2100},
-                                    {256, 160, 2, 355, 1800},
+                                    {256, 224, 2, 495, 2400},
+                                    {256, 192, 2, 440, 2100},
+                                    {256, 160, 2, 385, 1800},
                                     {128, 256, 1, 570, 2700},
                                     {128, 128, 1, 500, 1400},
                                     {128, 64, 1, 400, 800}};

@@ -21,6 +21,45 @@
 
 namespace b200 {
 
+// ---------------------------------------------------------------------------------------------
+// Launch timeline (builds with -DB200_GEMM_TIMELINE only; the macros are empty otherwise).
+// CTA 0 of every GEMM launch stamps clock64() at fixed points of its three roles into one row
+// of g_timeline (64 rows, used round-robin; slots 0 and 15 hold globaltimer values instead),
+// and every CTA stamps globaltimer at its first load, at the end of its main loop and at its
+// end into g_cta_times: where a launch spends its time between the dependency wait and the
+// last store, and how evenly the CTAs of a grid finish.  Read back by b200_gemm_debug_timeline /
+// b200_gemm_debug_cta_times (gemm_lib.cu) and printed by rocm_wmma_gemm_b200/timeline.py.
+//   0 entry (globaltimer)  1 entry  2 set-up done  3 dependency wait done (producer)
+//   4 first TMA load issued  5 last TMA load issued  6 first ring slot full (MMA thread)
+//   7 last accumulator committed  8 MMAs drained  9 accumulator seen by the epilogue
+//   10 first store issued  11 last store issued  12 staging buffers read  13 tail barrier
+//   14 TMEM freed  15 producer ready to wait (globaltimer)
+//   cluster K partitions: 16 before / 17 after the first cluster barrier  18 partials sent
+//   19 after the second barrier  20 sums stored  21 staging buffers read
+// ---------------------------------------------------------------------------------------------
+#ifdef B200_GEMM_TIMELINE
+constexpr int TIMELINE_ROWS = 64, TIMELINE_SLOTS = 24, TIMELINE_CTAS = 1024;
+__device__ unsigned long long g_timeline[TIMELINE_ROWS * TIMELINE_SLOTS];
+__device__ unsigned int       g_timeline_count;
+__device__ unsigned long long g_cta_times[3 * TIMELINE_CTAS];
+#define B200_TL(slot)                                                   \
+    do {                                                                \
+        if (blockIdx.x == 0) g_timeline[tl_base + (slot)] = clock64(); \
+    } while (0)
+#define B200_TLG(slot)                                                                 \
+    do {                                                                               \
+        if (blockIdx.x == 0) g_timeline[tl_base + (slot)] = ptx::global_timer_ns();   \
+    } while (0)
+#define B200_TL_CTA(row)                                                                                         \
+    do {                                                                                                         \
+        if (blockIdx.x < TIMELINE_CTAS) g_cta_times[(row) * TIMELINE_CTAS + blockIdx.x] = ptx::global_timer_ns(); \
+    } while (0)
+#else
+#define B200_TL(slot) do { } while (0)
+#define B200_TLG(slot) do { } while (0)
+#define B200_TL_CTA(row) do { } while (0)
+#endif
+
 // Output element kinds of the epilogue.
 enum : int { OUT_F32 = 0, OUT_F16 = 1, OUT_BF16 = 2 };
 
@@ -460,6 +499,16 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
     static_assert(SUB_ROWS >= 16, "each CTA stages at least 16 rows of B' per sub-tile");
     // (an MN-major B' is loaded in 64-row boxes: the host only picks BN >= 64 * CL for it)
 
+#ifdef B200_GEMM_TIMELINE
+    __shared__ uint32_t s_tl_base;
+    if (blockIdx.x == 0 && threadIdx.x == 0) s_tl_base = (atomicAdd(&g_timeline_count, 1u) % TIMELINE_ROWS) * TIMELINE_SLOTS;
+    uint32_t tl_base = 0;
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        tl_base = s_tl_base;
+        B200_TLG(0);
+        B200_TL(1);
+    }
+#endif
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t s_full[TR ? MAX_SLAB_STAGES : MAX_STAGES];
     __shared__ __align__(8) uint64_t s_empty[TR ? MAX_SLAB_STAGES : MAX_STAGES];
@@ -539,6 +588,10 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
         ptx::cluster_wait();
     }
     ptx::tc_fence_after();
+#ifdef B200_GEMM_TIMELINE
+    tl_base = s_tl_base;
+    if (threadIdx.x == 0) B200_TL(2);
+#endif
     const uint32_t tmem_base = s_tmem_base;
     // Programmatic dependent launch, both directions.  This grid may have been scheduled while
     // the kernel before it in the stream was still draining: everything above touched only this
@@ -600,7 +653,12 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                         const uint32_t sb  = sa + kc * a_bytes;
                         const uint32_t bar = ptx::smem_u32(&s_full[stage]);
                         ptx::mbar_expect_tx(bar, pitch);
+                        if (issued == 0) B200_TLG(15);
                         dep_wait();
+                        if (issued == 0) {
+                            B200_TL(3);
+                            B200_TL_CTA(0);
+                        }
                         if (p.a_mn_major == 0u) {
                             if (p.k4d) ptx::tma_load_4d(sa, &tmA, bar, 0, am, kb, c.z_in, pol_a);
                             else ptx::tma_load_3d(sa, &tmA, bar, k0, am, c.z_in, pol_a);
@@ -616,7 +674,9 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                             for (int j = 0; j < SUB_ROWS / 64; ++j)
                                 ptx::tma_load_3d(sb + j * half, &tmB, bar, bn + j * 64, k0, c.z_in, pol_b);
                         }
+                        if (issued == 0) B200_TL(4);
                         ++issued;
+                        B200_TL(5);
                         if (++stage == stages) {
                             stage = 0;
                             phase ^= 1u;
@@ -647,7 +707,12 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                     } else {
                         ptx::mbar_expect_tx(bar, step_bytes);
                     }
+                    if (issued == 0) B200_TLG(15);
                     dep_wait();
+                    if (issued == 0) {
+                        B200_TL(3);
+                        B200_TL_CTA(0);
+                    }
                     if (p.a_mn_major == 0u) {
                         tma_load<CL>(sa, &tmA, bar, k0, am, c.z_in, pol_a);
                     } else {
@@ -671,7 +736,9 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                                                  k0, c.z_in, pol_b);
                         }
                     }
+                    if (issued == 0) B200_TL(4);
                     ++issued;
+                    B200_TL(5);
                     if (++stage == stages) {
                         stage = 0;
                         phase ^= 1u;
@@ -765,6 +832,7 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                         ok = step(std::integral_constant<uint32_t, 2u>{}, 0u, (nkb > stg_x || i > 0u) ? 1u : 0u);
                     if (!ok) break;
                     umma_arrive<CL>(ptx::smem_u32(&s_tfull[1])); // half 1 complete
+                    B200_TL(7);
                     continue;
                 }
                 const uint32_t buf    = it % NUM_ACC;
@@ -787,6 +855,7 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                         ok = bounded_wait(ptx::smem_u32(&s_full[stage]), phase, &s_abort, p.status,
                                           ST_MMA_WAIT_FULL);
                         if (!ok) break;
+                        if (i == 0 && it == 0) B200_TL(6);
                         ptx::tc_fence_after();
                         const uint32_t sa = ring + stage * pitch;
                         const uint32_t sb = sa + kc * a_bytes;
@@ -810,6 +879,7 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                         ok = bounded_wait(ptx::smem_u32(&s_full[stage]), phase, &s_abort, p.status,
                                           ST_MMA_WAIT_FULL);
                         if (!ok) break;
+                        if (kb == c.kb0 && it == 0) B200_TL(6);
                         ptx::tc_fence_after();
                         const uint32_t sa = ring + stage * pitch;
                         const uint32_t sb = sa + a_bytes;
@@ -830,6 +900,7 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                 }
                 if (!ok) break;
                 umma_arrive<CL>(ptx::smem_u32(&s_tfull[buf])); // accumulator complete
+                B200_TL(7);
             }
             // All MMAs must have retired before TMEM is released and shared memory goes away.
             if constexpr (CL == 2) ptx::umma_commit_pair(ptx::smem_u32(&s_drain), 0x1);
@@ -841,6 +912,7 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                     break;
                 }
             }
+            B200_TL(8);
         }
     } else {
         // ------------------------------------------------------------------ epilogue
@@ -860,6 +932,10 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                 ptx::tc_fence_after();
                 ks_c  = c;
                 ks_ok = ok;
+                if (warp == 2 && lane == 0) {
+                    B200_TL(9);
+                    B200_TL_CTA(2);
+                }
             }
         } else
         for (; ok && work_next(p, cur, unit, units, wn, tile_m, c); ++it) {
@@ -877,6 +953,10 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                               ST_EPI_WAIT);
             ok = __all_sync(0xffffffffu, ok); // warp-uniform: the TMEM loads below are aligned
             if (!ok) break;
+            if (warp == 2 && lane == 0 && it == 0) {
+                B200_TL(9);
+                B200_TL_CTA(2);
+            }
             ptx::tc_fence_after();
             const uint32_t row0     = c.m0 + rank * BLOCK_M + q * 32u;
             // 32-row groups at and beyond the slab height belong to the next tile (narrow staged
@@ -989,6 +1069,10 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                             ptx::tma_store_3d(tm, sbuf, col0, row0, c.z_out, pol_d);
                         }
                         ptx::tma_store_commit();
+                        if (warp == 2) {
+                            if (nstore == 0) B200_TL(10);
+                            B200_TL(11);
+                        }
                     }
                     ++nstore;
                 }
@@ -1006,6 +1090,7 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
         // The staging buffers may go away once the stores have READ them; the writes themselves
         // are complete when the grid is (and a dependent grid waits for exactly that).
         if (lane == 0) ptx::tma_store_wait_read<0>();
+        if (warp == 2 && lane == 0) B200_TL(12);
     }
 
     if constexpr (KS) {
@@ -1027,8 +1112,10 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
         const uint32_t q    = warp & 3u;
         const uint32_t tacc = tmem_base + ((q * 32u) << 16);
         __syncwarp();
+        if (warp == 2 && lane == 0) B200_TL(16);
         ptx::cluster_arrive();
         ptx::cluster_wait();
+        if (warp == 2 && lane == 0) B200_TL(17);
         if (warp >= 2 && ks_ok) {
 #pragma unroll 1
             for (uint32_t ch = 0; ch < static_cast<uint32_t>(NCH); ++ch) {
@@ -1050,8 +1137,10 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
             }
         }
         __syncwarp();
+        if (warp == 2 && lane == 0) B200_TL(18);
         ptx::cluster_arrive();
         ptx::cluster_wait();
+        if (warp == 2 && lane == 0) B200_TL(19);
         if (warp >= 2 && ks_ok) {
             const uint32_t stg      = epi + q * 2u * EPI_BUF_BYTES;
             const uint32_t row0     = ks_c.m0 + q * 32u;
@@ -1139,7 +1228,9 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
                 }
                 } // staged store
             }
+            if (warp == 2 && lane == 0) B200_TL(20);
             if (lane == 0) ptx::tma_store_wait_read<0>();
+            if (warp == 2 && lane == 0) B200_TL(21);
         }
     }
 
@@ -1150,10 +1241,13 @@ __device__ __forceinline__ void gemm_umma_body(const CUtensorMap& tmA, const CUt
         ptx::cluster_arrive();
         ptx::cluster_wait();
     }
+    if (threadIdx.x == 0) B200_TL(13);
+    if (threadIdx.x == 64) B200_TL_CTA(1);
     if (warp == 1) {
         ptx::tc_fence_after();
         __syncwarp();
         ptx::tmem_dealloc<CL>(tmem_base, TMEM_COLS);
+        if (lane == 0) B200_TL(14);
     }
 }
 

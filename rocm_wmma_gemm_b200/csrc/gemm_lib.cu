@@ -1819,4 +1819,34 @@ extern "C" int b200_gemm_splitk_static(int types, void* C, const void* A, const 
     }
 }
 
+#ifdef B200_GEMM_TIMELINE
+// Timeline builds only (see gemm_kernels.cuh): copies of the stamps, after a device synchronise
+// (b200_gemm_debug_reset clears them).
+// `out` holds TIMELINE_ROWS x TIMELINE_SLOTS values, `count` the launches stamped so far (row of
+// launch i: i % TIMELINE_ROWS); `cta` holds 3 x TIMELINE_CTAS globaltimer values (first load,
+// end of main loop, end) of the last launch's CTAs.
+extern "C" int b200_gemm_debug_timeline(unsigned long long* out, unsigned int* count)
+{
+    if (cudaDeviceSynchronize() != cudaSuccess) return B200_GEMM_ERR_CUDA;
+    if (cudaMemcpyFromSymbol(out, b200::g_timeline, sizeof(b200::g_timeline)) != cudaSuccess) return B200_GEMM_ERR_CUDA;
+    if (cudaMemcpyFromSymbol(count, b200::g_timeline_count, sizeof(unsigned int)) != cudaSuccess) return B200_GEMM_ERR_CUDA;
+    return B200_GEMM_OK;
+}
+extern "C" int b200_gemm_debug_reset()
+{
+    if (cudaDeviceSynchronize() != cudaSuccess) return B200_GEMM_ERR_CUDA;
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, b200::g_timeline) != cudaSuccess || cudaMemset(p, 0, sizeof(b200::g_timeline)) != cudaSuccess) return B200_GEMM_ERR_CUDA;
+    if (cudaGetSymbolAddress(&p, b200::g_cta_times) != cudaSuccess || cudaMemset(p, 0, sizeof(b200::g_cta_times)) != cudaSuccess) return B200_GEMM_ERR_CUDA;
+    if (cudaGetSymbolAddress(&p, b200::g_timeline_count) != cudaSuccess || cudaMemset(p, 0, sizeof(unsigned int)) != cudaSuccess) return B200_GEMM_ERR_CUDA;
+    return B200_GEMM_OK;
+}
+extern "C" int b200_gemm_debug_cta_times(unsigned long long* cta)
+{
+    if (cudaDeviceSynchronize() != cudaSuccess) return B200_GEMM_ERR_CUDA;
+    if (cudaMemcpyFromSymbol(cta, b200::g_cta_times, sizeof(b200::g_cta_times)) != cudaSuccess) return B200_GEMM_ERR_CUDA;
+    return B200_GEMM_OK;
+}
+#endif
+
 #include "slab_driver.inc"

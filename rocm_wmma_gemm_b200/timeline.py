@@ -99,7 +99,9 @@ def run(lib, type_name: str, M: int, N: int, K: int, layouts=(0, 1, 0), launches
         rel.append(stamped(a[1:15]))
         nxt.append(b[0] - a[0])
         ks.append(stamped(a[16:22]))
-    with np.errstate(all="ignore"):
+    import warnings
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore", RuntimeWarning)   # a column of points this kernel never passes is all NaN
         rel, ks = np.nanmedian(np.array(rel), axis=0), np.nanmedian(np.array(ks), axis=0)
     cta = (ctypes.c_ulonglong * (3 * CTAS))()
     if lib.b200_gemm_debug_cta_times(cta) != 0:
